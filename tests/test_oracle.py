@@ -1,0 +1,100 @@
+"""The CPU oracle against fixtures produced by the reference itself
+(tests/golden/make_golden.py) and against the structural known-answer facts of
+the reference's own C++ test (layers/test.cpp:80-164)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from oracle import EncoderConfig
+
+
+def test_tables_match_reference_bit_exact(golden_dir):
+    z = np.load(os.path.join(golden_dir, "tables.npz"))
+    n = 0
+    for key in z.files:
+        s, h, L, m = key.split("_")
+        seed, heads, L, max_pos = int(s[1:]), int(h[1:]), int(L[1:]), int(m[1:])
+        ref = z[key]
+        if int(ref.max()) >= L:
+            with pytest.raises(oracle.UnsupportedLength):
+                oracle.rand_block_table(seed, heads, L, 3, max_pos)
+            continue
+        got = oracle.rand_block_table(seed, heads, L, 3, max_pos)
+        assert got.shape == ref.shape and np.array_equal(got, ref), key
+        n += 1
+    assert n > 200
+
+
+def test_twelve_blocks_is_rejected():
+    with pytest.raises(oracle.UnsupportedLength):
+        oracle.rand_block_table(0, 12, 12, 3, 4096)
+
+
+def test_hidden_states_small_model(golden_dir):
+    z = np.load(os.path.join(golden_dir, "hidden_small.npz"))
+    cfg = EncoderConfig(hidden=128, heads=2, ffn=256, layers=2, max_pos=4096, vocab=97)
+    P = oracle.make_weights(cfg, seed=3, nonzero_bias=True)
+    for L in (8, 13, 16, 20):
+        g = torch.Generator().manual_seed(100 + L)
+        h = torch.randn(L * 64, cfg.hidden, generator=g)
+        for i in range(cfg.layers):
+            h = oracle.layer_ref(h, P, i, cfg)
+            ref = torch.from_numpy(z[f"L{L}_layer{i}"])
+            assert (h[::4] - ref).abs().max().item() < 2e-5, (L, i)
+
+
+def test_hidden_states_base_layer(golden_dir):
+    z = np.load(os.path.join(golden_dir, "hidden_base.npz"))
+    cfg = EncoderConfig(layers=1)
+    P = oracle.make_weights(cfg, seed=0, embeddings=False)
+    for L in (13, 16):
+        g = torch.Generator().manual_seed(200 + L)
+        x = torch.randn(L * 64, cfg.hidden, generator=g)
+        o = oracle.layer_ref(x, P, 0, cfg)
+        assert (o[::16] - torch.from_numpy(z[f"L{L}_rows"])).abs().max().item() < 5e-5
+        s = z[f"L{L}_sum"]
+        assert abs(o.double().abs().sum().item() - s[1]) / s[1] < 1e-6
+
+
+def test_embeddings(golden_dir):
+    z = np.load(os.path.join(golden_dir, "embeddings.npz"))
+    cfg = EncoderConfig(hidden=128, heads=2, ffn=256, layers=2, max_pos=4096, vocab=97)
+    P = oracle.make_weights(cfg, seed=3, nonzero_bias=True)
+    e = oracle.embeddings_ref(torch.from_numpy(z["ids"]), P, cfg)
+    assert (e - torch.from_numpy(z["out"])).abs().max().item() < 1e-5
+
+
+def test_csr_structure_of_reference_fixture():
+    # layers/test.cpp:80-91: one 64-block sequence -> 65 offsets 0,64,71,79,...,558,622
+    cfg = EncoderConfig()
+    ptr, idx = oracle.build_block_csr([4096], cfg, layer=0)
+    assert ptr.shape == (65,) and idx.shape == (12, 622)
+    assert list(ptr[:4]) == [0, 64, 71, 79] and list(ptr[-3:]) == [551, 558, 622]
+    assert list(idx[0, :64]) == list(range(64)) and list(idx[5, -64:]) == list(range(64))
+    assert oracle.visits_per_head([4096], cfg) == 622
+
+
+def test_full_attention_and_band_lists():
+    cfg = EncoderConfig()
+    ptr, idx = oracle.build_block_csr([512, 704], cfg, layer=0)
+    assert ptr[-1] == 8 * 8 + 11 * 11
+    band = EncoderConfig(pattern="band", band_half=4)
+    lists = oracle.kv_block_lists(20, band, None, 0)
+    assert lists[0] == list(range(20))
+    assert lists[3] == list(range(0, 8))
+    assert lists[10] == [0] + list(range(6, 15))
+    assert lists[19] == [0] + list(range(15, 20))
+
+
+def test_lpt_partition_matches_reference_layout():
+    # python/util.py:36-50 cost array for one 64-block sequence; layers/test.cpp:95-107
+    # lists 161 offsets for 160 CTAs and 768 work items.
+    L = 64
+    cost = [L, 7] + [8] * (L - 4) + [7, L]
+    off, ids = oracle.lpt_partition(cost, [0, L], 160, 12)
+    assert len(off) == 161 and len(ids) == 768 and sorted(ids) == list(range(768))
+    # the two 64-visit rows of each head are placed first, one per CTA
+    assert ids[off[0]:off[0] + 1] == [0] and off[1] - off[0] >= 1
