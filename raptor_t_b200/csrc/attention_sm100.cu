@@ -1,0 +1,467 @@
+// Block-sparse attention for sm_100a (tcgen05 + TMEM + TMA), online softmax fused.
+//
+// A persistent CTA walks its list of work items.  An item is up to two 64-token
+// query blocks of one (sequence, head) stacked into a 128-row tile, plus the
+// merged list of 64-token key/value blocks they attend to (global, window and
+// random blocks come from the same table; each entry carries a 2-bit mask that
+// says which of the two query blocks uses it).
+//
+//   warp 4   TMA producer: Q tile per item, then one K box and one V box
+//            (64 x 64, 128-byte swizzle) per list entry into a shared-memory ring;
+//   warp 5   MMA issuer:   S = Q K^T  (M=128, N=64, K=64; both operands K-major in
+//            shared memory) into one of two TMEM score buffers, and
+//            PV = P V (P read from TMEM, V MN-major in shared memory) into one of
+//            two TMEM result buffers.  S of entry j+1 is issued before PV of entry j;
+//   warps 0-3  softmax: thread r owns tile row r.  It pulls its score row out of
+//            TMEM, keeps the running max / sum in fp32 (base-2 exponentials), writes
+//            the 16-bit probabilities back to TMEM for the PV MMA, then folds the
+//            previous entry's PV result into its fp32 output row held in registers.
+//
+// Output rows go token-major [T][heads*64].  Counterpart of
+// layers/kernels/sparse_attention.cu:2953-3228; the math follows the reference's
+// validation model (python/modeling_big_bird.py:626-851: softmax over the
+// concatenated listed blocks, duplicates counted twice).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <algorithm>
+#include <vector>
+
+#include "attention.h"
+#include "common.h"
+#include "device_error.h"
+#include "launch_count.h"
+#include "sm100_ptx.cuh"
+#include "tma_host.h"
+
+namespace rt {
+namespace {
+
+using namespace ptx;
+
+constexpr int kThreads = 192;
+constexpr int kStages = 4;               // K/V ring depth
+constexpr int kTileBytes = 64 * 64 * 2;  // one 64 x 64 16-bit block
+constexpr int kQBytes = 2 * kTileBytes;
+constexpr int kTmemCols = 512;
+constexpr int kColS = 0;     // 2 x 64 fp32 score columns
+constexpr int kColP = 128;   // 2 x 32 columns of packed 16-bit probabilities
+constexpr int kColPV = 192;  // 2 x 64 fp32 result columns
+
+struct Smem {
+  uint8_t q[2][kQBytes];
+  uint8_t k[kStages][kTileBytes];
+  uint8_t v[kStages][kTileBytes];
+  uint64_t q_full[2], q_empty[2];
+  uint64_t k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
+  uint64_t s_full[2], s_free[2], p_full[2], pv_full[2], pv_free[2];
+  uint32_t tmem_slot;
+  int abort_flag;
+};
+constexpr int kSmemBytes = sizeof(Smem) + 1024;
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  if constexpr (BF16) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  } else {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(kThreads, 1)
+sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                        const __grid_constant__ CUtensorMap map_v, uint16_t* __restrict__ ctx,
+                        const AttnItem* __restrict__ items, const int32_t* __restrict__ entries,
+                        const int32_t* __restrict__ cta_ptr, int hidden, float scale_log2, int* error_flag) {
+  extern __shared__ uint8_t smem_raw[];
+  Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&sm.q_full[i], 1);
+      mbar_init(&sm.q_empty[i], 1);
+      mbar_init(&sm.s_full[i], 1);
+      mbar_init(&sm.s_free[i], 128);
+      mbar_init(&sm.p_full[i], 128);
+      mbar_init(&sm.pv_full[i], 1);
+      mbar_init(&sm.pv_free[i], 128);
+    }
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&sm.k_full[s], 1);
+      mbar_init(&sm.k_empty[s], 1);
+      mbar_init(&sm.v_full[s], 1);
+      mbar_init(&sm.v_empty[s], 1);
+    }
+    sm.abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(&sm.tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = sm.tmem_slot;
+  AbortCtx ab{&sm.abort_flag, error_flag};
+
+  const int item_begin = cta_ptr[blockIdx.x];
+  const int item_end = cta_ptr[blockIdx.x + 1];
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      prefetch_tensormap(&map_q);
+      prefetch_tensormap(&map_k);
+      prefetch_tensormap(&map_v);
+      uint32_t g = 0, itn = 0;
+      bool ok = true;
+      for (int it = item_begin; it < item_end && ok; ++it, ++itn) {
+        const AttnItem item = items[it];
+        const int qb = itn & 1;
+        if (!mbar_wait(&sm.q_empty[qb], ((itn >> 1) & 1) ^ 1, ab, 201)) break;
+        mbar_arrive_expect_tx(&sm.q_full[qb], kQBytes);
+        tma_load_2d(sm.q[qb], &map_q, 0, item.q_row0, &sm.q_full[qb]);
+        tma_load_2d(sm.q[qb] + kTileBytes, &map_q, 0, item.q_row1, &sm.q_full[qb]);
+        for (int j = 0; j < item.n_entries; ++j, ++g) {
+          const int s = g % kStages;
+          const uint32_t ph = (g / kStages) & 1;
+          const int row = item.kv_row0 + (entries[item.entry_off + j] >> 2) * 64;
+          if (!mbar_wait(&sm.k_empty[s], ph ^ 1, ab, 202)) { ok = false; break; }
+          mbar_arrive_expect_tx(&sm.k_full[s], kTileBytes);
+          tma_load_2d(sm.k[s], &map_k, 0, row, &sm.k_full[s]);
+          if (!mbar_wait(&sm.v_empty[s], ph ^ 1, ab, 203)) { ok = false; break; }
+          mbar_arrive_expect_tx(&sm.v_full[s], kTileBytes);
+          tma_load_2d(sm.v[s], &map_v, 0, row, &sm.v_full[s]);
+        }
+      }
+      // A wait gives up only after the pipeline has been idle for the whole time-out,
+      // so none of this thread's copies can still be in flight when it gets here.
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_f16(128, 64, BF16 ? 1 : 0, false);
+      constexpr uint32_t idesc_pv = make_idesc_f16(128, 64, BF16 ? 1 : 0, true);
+      // two cursors over the flattened (item, entry) stream: S runs one entry ahead of PV
+      int s_item = item_begin, s_j = 0, s_n = 0;
+      uint32_t s_g = 0, s_itn = 0;
+      int pv_item = item_begin, pv_j = 0, pv_n = 0;
+      uint32_t pv_g = 0;
+      bool ok = true;
+      auto skip_empty = [&](int& item, int& n) {
+        while (item < item_end && (n = items[item].n_entries) == 0) ++item;
+      };
+      skip_empty(s_item, s_n);
+      skip_empty(pv_item, pv_n);
+
+      auto issue_s = [&]() -> bool {
+        const int qb = s_itn & 1;
+        if (s_j == 0) {
+          if (!mbar_wait(&sm.q_full[qb], (s_itn >> 1) & 1, ab, 211)) return false;
+        }
+        const int b = s_g & 1;
+        const uint32_t u = s_g >> 1;
+        const int st = s_g % kStages;
+        const uint32_t ph = (s_g / kStages) & 1;
+        if (!mbar_wait(&sm.k_full[st], ph, ab, 212)) return false;
+        if (!mbar_wait(&sm.s_free[b], (u & 1) ^ 1, ab, 213)) return false;
+        tc_fence_after_sync();
+        const uint64_t dq = make_smem_desc_sw128(smem_u32(sm.q[qb]));
+        const uint64_t dk = make_smem_desc_sw128(smem_u32(sm.k[st]));
+        const uint32_t d = tmem_base + kColS + b * 64;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) mma_ss(d, dq + (k * 32 >> 4), dk + (k * 32 >> 4), idesc_s, k ? 1u : 0u);
+        tc_commit(&sm.k_empty[st]);
+        tc_commit(&sm.s_full[b]);
+        ++s_g;
+        if (++s_j == s_n) {
+          tc_commit(&sm.q_empty[qb]);
+          ++s_itn;
+          ++s_item;
+          s_j = 0;
+          skip_empty(s_item, s_n);
+        }
+        return true;
+      };
+      auto issue_pv = [&]() -> bool {
+        const int b = pv_g & 1;
+        const uint32_t u = pv_g >> 1;
+        const int st = pv_g % kStages;
+        const uint32_t ph = (pv_g / kStages) & 1;
+        if (!mbar_wait(&sm.v_full[st], ph, ab, 214)) return false;
+        if (!mbar_wait(&sm.pv_free[b], (u & 1) ^ 1, ab, 215)) return false;
+        if (!mbar_wait(&sm.p_full[b], u & 1, ab, 216)) return false;
+        tc_fence_after_sync();
+        const uint64_t dv = make_smem_desc_sw128(smem_u32(sm.v[st]));
+        const uint32_t d = tmem_base + kColPV + b * 64;
+        const uint32_t a = tmem_base + kColP + b * 32;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) mma_ts(d, a + k * 8, dv + (k * 2048 >> 4), idesc_pv, k ? 1u : 0u);
+        tc_commit(&sm.v_empty[st]);
+        tc_commit(&sm.pv_full[b]);
+        ++pv_g;
+        if (++pv_j == pv_n) {
+          ++pv_item;
+          pv_j = 0;
+          skip_empty(pv_item, pv_n);
+        }
+        return true;
+      };
+
+      if (s_item < item_end) ok = issue_s();
+      while (ok && pv_item < item_end) {
+        if (s_item < item_end) ok = issue_s();
+        if (ok) ok = issue_pv();
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax warps 0..3
+    const int row = warp * 32 + lane;  // tile row == TMEM lane
+    const int half = row >> 6;         // 0: query block A, 1: query block B
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+    uint32_t g = 0;
+    bool ok = true;
+    for (int it = item_begin; it < item_end && ok; ++it) {
+      const AttnItem item = items[it];
+      const int n = item.n_entries;
+      if (n == 0) continue;
+      float o[64];
+#pragma unroll
+      for (int i = 0; i < 64; ++i) o[i] = 0.f;
+      float m = -INFINITY, l = 0.f;
+      bool prev_active = false;
+      for (int j = 0; j <= n && ok; ++j) {
+        float alpha = 1.f;
+        bool active = false;
+        if (j < n) {
+          const uint32_t gj = g + j;
+          const int b = gj & 1;
+          const uint32_t u = gj >> 1;
+          active = ((entries[item.entry_off + j] >> half) & 1) != 0;
+          if (!mbar_wait(&sm.s_full[b], u & 1, ab, 221)) { ok = false; break; }
+          tc_fence_after_sync();
+          uint32_t p[32];
+          if (active) {
+            uint32_t s[64];
+            tmem_ld32(lane_base + kColS + b * 64, s);
+            tmem_ld32(lane_base + kColS + b * 64 + 32, s + 32);
+            tc_wait_ld();
+            tc_fence_before_sync();
+            mbar_arrive(&sm.s_free[b]);
+            float mx = __uint_as_float(s[0]);
+#pragma unroll
+            for (int i = 1; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(s[i]));
+            const float m_new = fmaxf(m, mx * scale_log2);
+            alpha = ex2(m - m_new);
+            float sum = 0.f;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float p0 = ex2(fmaf(__uint_as_float(s[2 * i]), scale_log2, -m_new));
+              const float p1 = ex2(fmaf(__uint_as_float(s[2 * i + 1]), scale_log2, -m_new));
+              sum += p0 + p1;
+              p[i] = pack2<BF16>(p0, p1);
+            }
+            l = l * alpha + sum;
+            m = m_new;
+          } else {
+            tc_fence_before_sync();
+            mbar_arrive(&sm.s_free[b]);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) p[i] = 0u;
+          }
+          tmem_st32(lane_base + kColP + b * 32, p);
+          tc_wait_st();
+          tc_fence_before_sync();
+          mbar_arrive(&sm.p_full[b]);
+        }
+        if (j > 0) {
+          const uint32_t gp = g + j - 1;
+          const int bp = gp & 1;
+          const uint32_t up = gp >> 1;
+          if (!mbar_wait(&sm.pv_full[bp], up & 1, ab, 222)) { ok = false; break; }
+          tc_fence_after_sync();
+          if (prev_active) {
+            uint32_t r[64];
+            tmem_ld32(lane_base + kColPV + bp * 64, r);
+            tmem_ld32(lane_base + kColPV + bp * 64 + 32, r + 32);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 64; ++i) o[i] += __uint_as_float(r[i]);
+          }
+          tc_fence_before_sync();
+          mbar_arrive(&sm.pv_free[bp]);
+        }
+        if (alpha != 1.f) {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) o[i] *= alpha;
+        }
+        prev_active = active;
+      }
+      g += n;
+      if (!ok) break;
+      const int tok0 = half == 0 ? item.out_tok0 : item.out_tok1;
+      if (tok0 >= 0) {
+        const float inv = 1.0f / l;
+        uint4* dst = reinterpret_cast<uint4*>(ctx + static_cast<size_t>(tok0 + (row & 63)) * hidden + item.head * 64);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          uint4 v;
+          v.x = pack2<BF16>(o[8 * q + 0] * inv, o[8 * q + 1] * inv);
+          v.y = pack2<BF16>(o[8 * q + 2] * inv, o[8 * q + 3] * inv);
+          v.z = pack2<BF16>(o[8 * q + 4] * inv, o[8 * q + 5] * inv);
+          v.w = pack2<BF16>(o[8 * q + 6] * inv, o[8 * q + 7] * inv);
+          dst[q] = v;
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace
+
+rt_status launch_sparse_attention(void* ctx, const void* q, const void* k, const void* v, const AttnItem* items_dev,
+                                  const int32_t* entries_dev, const int32_t* cta_ptr_dev, int n_ctas,
+                                  int total_tokens, int heads, float scale, int dtype, cudaStream_t st) {
+  RT_REQUIRE(dtype == RT_F16 || dtype == RT_BF16, RT_ERR_INVALID, "sparse_attention: unknown dtype %d", dtype);
+  RT_REQUIRE(n_ctas > 0 && total_tokens > 0 && heads > 0, RT_ERR_INVALID, "sparse_attention: empty plan");
+  const uint64_t rows = static_cast<uint64_t>(total_tokens) * heads;
+  CUtensorMap mq, mk, mv;
+  RT_TRY(make_tensor_map_2d(&mq, q, rows, 64, 64, 64, 64, true));
+  RT_TRY(make_tensor_map_2d(&mk, k, rows, 64, 64, 64, 64, true));
+  RT_TRY(make_tensor_map_2d(&mv, v, rows, 64, 64, 64, 64, true));
+  int* err = device_error_word();
+  RT_REQUIRE(err != nullptr, RT_ERR_CUDA, "sparse_attention: cannot allocate the device error word");
+  const float scale_log2 = scale * 1.4426950408889634f;
+  const int hidden = heads * 64;
+  if (dtype == RT_BF16) {
+    static bool set = false;
+    if (!set) {
+      RT_CHECK_CUDA(cudaFuncSetAttribute(sparse_attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kSmemBytes));
+      set = true;
+    }
+    sparse_attention_kernel<true><<<n_ctas, kThreads, kSmemBytes, st>>>(mq, mk, mv, (uint16_t*)ctx, items_dev,
+                                                                         entries_dev, cta_ptr_dev, hidden, scale_log2,
+                                                                         err);
+  } else {
+    static bool set = false;
+    if (!set) {
+      RT_CHECK_CUDA(cudaFuncSetAttribute(sparse_attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kSmemBytes));
+      set = true;
+    }
+    sparse_attention_kernel<false><<<n_ctas, kThreads, kSmemBytes, st>>>(mq, mk, mv, (uint16_t*)ctx, items_dev,
+                                                                          entries_dev, cta_ptr_dev, hidden, scale_log2,
+                                                                          err);
+  }
+  count_launch();
+  RT_CHECK_CUDA(cudaGetLastError());
+  return RT_OK;
+}
+
+}  // namespace rt
+
+// ---------------------------------------------------------------------------------------------
+// C ABI: stand-alone attention plan + launch
+// ---------------------------------------------------------------------------------------------
+using namespace rt;
+
+struct rt_attn_plan {
+  AttnPlanHost host;
+  uint8_t* dev = nullptr;
+  size_t items_off = 0, entries_off = 0, cta_off = 0, bytes = 0;
+  int n_ctas = 0;
+  int dtype = 0;
+};
+
+extern "C" rt_status rt_attn_plan_create(const rt_config* cfg, const int32_t* lens, int n_seq, const int32_t* kv_ptr,
+                                         const int32_t* kv_idx, int n_ctas, void* stream, rt_attn_plan** out) {
+  RT_REQUIRE(cfg && lens && kv_ptr && kv_idx && out, RT_ERR_INVALID, "attn_plan_create: null pointer");
+  RT_TRY(check_config(cfg));
+  RT_TRY(validate_lengths(*cfg, lens, n_seq));
+  if (n_ctas <= 0) {
+    int dev = 0;
+    RT_CHECK_CUDA(cudaGetDevice(&dev));
+    RT_CHECK_CUDA(cudaDeviceGetAttribute(&n_ctas, cudaDevAttrMultiProcessorCount, dev));
+  }
+  int nblk = 0;
+  for (int s = 0; s < n_seq; ++s) nblk += lens[s] / cfg->block;
+  const int64_t visits = kv_ptr[nblk];
+  auto* p = new rt_attn_plan();
+  rt_status s = build_attn_plan(*cfg, lens, n_seq, kv_ptr, kv_idx, visits, n_ctas, p->host);
+  if (s != RT_OK) {
+    delete p;
+    return s;
+  }
+  p->n_ctas = n_ctas;
+  auto align = [](size_t x) { return (x + 255) & ~size_t(255); };
+  p->items_off = 0;
+  p->entries_off = align(p->host.items.size() * sizeof(AttnItem));
+  p->cta_off = p->entries_off + align(p->host.entries.size() * sizeof(int32_t));
+  p->bytes = p->cta_off + align(p->host.cta_ptr.size() * sizeof(int32_t));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMalloc(&p->dev, p->bytes);
+  if (e == cudaSuccess)
+    e = cudaMemcpyAsync(p->dev + p->items_off, p->host.items.data(), p->host.items.size() * sizeof(AttnItem),
+                        cudaMemcpyHostToDevice, st);
+  if (e == cudaSuccess)
+    e = cudaMemcpyAsync(p->dev + p->entries_off, p->host.entries.data(), p->host.entries.size() * sizeof(int32_t),
+                        cudaMemcpyHostToDevice, st);
+  if (e == cudaSuccess)
+    e = cudaMemcpyAsync(p->dev + p->cta_off, p->host.cta_ptr.data(), p->host.cta_ptr.size() * sizeof(int32_t),
+                        cudaMemcpyHostToDevice, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) {
+    if (p->dev) cudaFree(p->dev);
+    delete p;
+    return fail(RT_ERR_CUDA, "attn_plan_create: %s", cudaGetErrorString(e));
+  }
+  *out = p;
+  return RT_OK;
+}
+
+extern "C" rt_status rt_attn_plan_destroy(rt_attn_plan* p) {
+  if (!p) return RT_OK;
+  if (p->dev) cudaFree(p->dev);
+  delete p;
+  return RT_OK;
+}
+
+extern "C" rt_status rt_attn_plan_stats(const rt_attn_plan* p, int64_t* entries_out, int64_t* visits_out,
+                                        int32_t* items_out) {
+  RT_REQUIRE(p != nullptr, RT_ERR_INVALID, "attn_plan_stats: null plan");
+  if (entries_out) *entries_out = static_cast<int64_t>(p->host.entries.size());
+  if (visits_out) *visits_out = p->host.visits;
+  if (items_out) *items_out = static_cast<int32_t>(p->host.items.size());
+  return RT_OK;
+}
+
+extern "C" rt_status rt_sparse_attention(void* ctx, const void* q, const void* k, const void* v,
+                                         const rt_attn_plan* plan, float scale, int dtype, void* stream) {
+  RT_REQUIRE(ctx && q && k && v && plan, RT_ERR_INVALID, "sparse_attention: null pointer");
+  return launch_sparse_attention(ctx, q, k, v, reinterpret_cast<const AttnItem*>(plan->dev + plan->items_off),
+                                 reinterpret_cast<const int32_t*>(plan->dev + plan->entries_off),
+                                 reinterpret_cast<const int32_t*>(plan->dev + plan->cta_off), plan->n_ctas,
+                                 plan->host.total_tokens, plan->host.heads, scale, dtype,
+                                 static_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,295 @@
+// Persistent, warp-specialised tcgen05 GEMM for sm_100a:
+//     C[M][N] = A[M][K] * W[N][K]^T  (+ bias) (+ GELU),  16-bit in/out, fp32 accumulate.
+//
+// One CTA per SM walks 128 x BN output tiles.  Warp 0 streams A and W k-slices
+// (64 elements = one 128-byte swizzle atom) into a shared-memory ring with TMA;
+// warp 1 issues tcgen05.mma (M=128, N=BN, K=16) into one of two TMEM
+// accumulators; warps 2-5 drain the other accumulator (tcgen05.ld), apply the
+// epilogue and store, so the epilogue of tile i overlaps the main loop of
+// tile i+1.  Stands in for the cuBLAS calls of layers/kernels/mat_mul.cpp:58-76
+// (which accumulate in fp16; this kernel accumulates in fp32).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <algorithm>
+
+#include "common.h"
+#include "device_error.h"
+#include "launch_count.h"
+#include "sm100_ptx.cuh"
+#include "tma_host.h"
+
+namespace rt {
+namespace {
+
+using namespace ptx;
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;
+constexpr int kGemmThreads = 192;
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;  // power of two: 128, 256, 512
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ float gelu_tanh_f(float x) {
+  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+  return 0.5f * x * (1.0f + t);
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  if constexpr (BF16) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  } else {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+}
+template <bool BF16>
+__device__ __forceinline__ float2 unpack2(uint32_t w) {
+  if constexpr (BF16) {
+    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+  } else {
+    return __half22float2(*reinterpret_cast<__half2*>(&w));
+  }
+}
+
+template <int BN, bool BF16, int EPI>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+            uint16_t* __restrict__ C, const uint16_t* __restrict__ bias, int M, int N, int K, int* error_flag) {
+  using Cfg = GemmCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + Cfg::kStages;
+  uint64_t* acc_full = bars + 2 * Cfg::kStages;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 128);
+    }
+    *cta_abort = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  AbortCtx ab{cta_abort, error_flag};
+
+  const int n_tiles_n = N / BN;
+  const int n_tiles_m = (M + kBM - 1) / kBM;
+  const int n_tiles = n_tiles_m * n_tiles_n;
+  const int k_blocks = K / kBK;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      prefetch_tensormap(&map_a);
+      prefetch_tensormap(&map_w);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+        const int m0 = (t / n_tiles_n) * kBM, n0 = (t % n_tiles_n) * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % Cfg::kStages;
+          const uint32_t ph = (it / Cfg::kStages) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1, ab, 101)) { ok = false; break; }
+          uint8_t* sa = smem + s * Cfg::kStageBytes;
+          mbar_arrive_expect_tx(&full[s], Cfg::kStageBytes);
+          tma_load_2d(sa, &map_a, kb * kBK, m0, &full[s]);
+          tma_load_2d(sa + Cfg::kABytes, &map_w, kb * kBK, n0, &full[s]);
+        }
+      }
+      // A wait only gives up after the whole pipeline has been idle for the full
+      // time-out, so no copy issued by this thread can still be in flight here.
+      (void)ok;
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_f16(kBM, BN, BF16 ? 1 : 0, false);
+      uint32_t it = 0, tile_it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++tile_it) {
+        const int a = tile_it & 1;
+        const uint32_t aph = (tile_it >> 1) & 1;
+        if (!mbar_wait(&acc_empty[a], aph ^ 1, ab, 102)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + a * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % Cfg::kStages;
+          const uint32_t ph = (it / Cfg::kStages) & 1;
+          if (!mbar_wait(&full[s], ph, ab, 103)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + s * Cfg::kStageBytes);
+          const uint64_t da = make_smem_desc_sw128(sa);
+          const uint64_t db = make_smem_desc_sw128(sa + Cfg::kABytes);
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k)
+            mma_ss(d_tmem, da + (k * 32 >> 4), db + (k * 32 >> 4), idesc, (kb | k) ? 1u : 0u);
+          tc_commit(&empty[s]);
+        }
+        if (ok) tc_commit(&acc_full[a]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------- epilogue warps 2..5
+    const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;
+    uint32_t tile_it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++tile_it) {
+      const int a = tile_it & 1;
+      const uint32_t aph = (tile_it >> 1) & 1;
+      const int m0 = (t / n_tiles_n) * kBM, n0 = (t % n_tiles_n) * BN;
+      if (!mbar_wait(&acc_full[a], aph, ab, 104)) { ok = false; break; }
+      tc_fence_after_sync();
+      const int row = m0 + row_in_tile;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(taddr + c * 32, r);
+        tc_wait_ld();
+        uint32_t o[16];
+        if constexpr (EPI == RT_EPI_NONE) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) o[j] = pack2<BF16>(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+        } else {
+          const uint4* bv = reinterpret_cast<const uint4*>(bias + n0 + c * 32);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const uint4 b4 = __ldg(bv + q);
+            const uint32_t bw[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 bb = unpack2<BF16>(bw[j]);
+              float x0 = __uint_as_float(r[q * 8 + 2 * j]) + bb.x;
+              float x1 = __uint_as_float(r[q * 8 + 2 * j + 1]) + bb.y;
+              if constexpr (EPI == RT_EPI_BIAS_GELU) {
+                x0 = gelu_tanh_f(x0);
+                x1 = gelu_tanh_f(x1);
+              }
+              o[q * 4 + j] = pack2<BF16>(x0, x1);
+            }
+          }
+        }
+        if (row < M) {
+          uint4* dst = reinterpret_cast<uint4*>(C + static_cast<size_t>(row) * N + n0 + c * 32);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) dst[q] = make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&acc_empty[a]);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+int gemm_sm_count() {
+  int dev = 0, n = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  return n > 0 ? n : 148;
+}
+
+template <int BN, bool BF16, int EPI>
+rt_status launch(void* c, const void* a, const void* w, const void* bias, int M, int N, int K, cudaStream_t st) {
+  using Cfg = GemmCfg<BN>;
+  CUtensorMap ma, mw;
+  RT_TRY(make_tensor_map_2d(&ma, a, M, K, K, kBM, kBK, true));
+  RT_TRY(make_tensor_map_2d(&mw, w, N, K, K, BN, kBK, true));
+  auto kern = gemm_kernel<BN, BF16, EPI>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    RT_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    attr_set = true;
+  }
+  int* err = device_error_word();
+  RT_REQUIRE(err != nullptr, RT_ERR_CUDA, "gemm: cannot allocate the device error word");
+  const int tiles = ((M + kBM - 1) / kBM) * (N / BN);
+  const int grid = std::min(tiles, gemm_sm_count());
+  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, st>>>(ma, mw, (uint16_t*)c, (const uint16_t*)bias, M, N, K, err);
+  count_launch();
+  RT_CHECK_CUDA(cudaGetLastError());
+  return RT_OK;
+}
+
+template <int BN, bool BF16>
+rt_status launch_epi(void* c, const void* a, const void* w, const void* bias, int M, int N, int K, int epi,
+                     cudaStream_t st) {
+  switch (epi) {
+    case RT_EPI_NONE: return launch<BN, BF16, RT_EPI_NONE>(c, a, w, bias, M, N, K, st);
+    case RT_EPI_BIAS: return launch<BN, BF16, RT_EPI_BIAS>(c, a, w, bias, M, N, K, st);
+    case RT_EPI_BIAS_GELU: return launch<BN, BF16, RT_EPI_BIAS_GELU>(c, a, w, bias, M, N, K, st);
+  }
+  return fail(RT_ERR_INVALID, "gemm: unknown epilogue %d", epi);
+}
+
+}  // namespace
+
+}  // namespace rt
+
+using namespace rt;
+
+extern "C" rt_status rt_gemm(void* c, const void* a, const void* w, const void* bias, int M, int N, int K, int epilogue,
+                             int dtype, void* stream) {
+  RT_REQUIRE(c && a && w, RT_ERR_INVALID, "gemm: null pointer");
+  RT_REQUIRE(M >= 0 && N > 0 && K > 0 && N % 64 == 0 && K % 64 == 0, RT_ERR_INVALID,
+             "gemm: need N %% 64 == 0 and K %% 64 == 0 (got M=%d N=%d K=%d)", M, N, K);
+  RT_REQUIRE(epilogue == RT_EPI_NONE || bias != nullptr, RT_ERR_INVALID, "gemm: epilogue needs a bias vector");
+  RT_REQUIRE(((reinterpret_cast<uintptr_t>(c) | reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w) |
+               reinterpret_cast<uintptr_t>(bias)) & 15u) == 0,
+             RT_ERR_INVALID, "gemm: pointers must be 16-byte aligned");
+  RT_REQUIRE(dtype == RT_F16 || dtype == RT_BF16, RT_ERR_INVALID, "gemm: unknown dtype %d", dtype);
+  if (M == 0) return RT_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // largest tile width that divides N and still gives every SM a tile; else the narrowest
+  const int sms = 148;
+  const int mt = (M + kBM - 1) / kBM;
+  int bn = 64;
+  if (N % 256 == 0 && mt * (N / 256) >= sms) bn = 256;
+  else if (N % 128 == 0 && mt * (N / 128) >= sms) bn = 128;
+  const bool bf = dtype == RT_BF16;
+  if (bn == 256) return bf ? launch_epi<256, true>(c, a, w, bias, M, N, K, epilogue, st)
+                           : launch_epi<256, false>(c, a, w, bias, M, N, K, epilogue, st);
+  if (bn == 128) return bf ? launch_epi<128, true>(c, a, w, bias, M, N, K, epilogue, st)
+                           : launch_epi<128, false>(c, a, w, bias, M, N, K, epilogue, st);
+  return bf ? launch_epi<64, true>(c, a, w, bias, M, N, K, epilogue, st)
+            : launch_epi<64, false>(c, a, w, bias, M, N, K, epilogue, st);
+}

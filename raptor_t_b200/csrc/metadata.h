@@ -1,0 +1,85 @@
+// Host-side metadata of the block-sparse encoder: random-block tables (bit-exact
+// with numpy's legacy RandomState, which the reference's validation model uses),
+// CSR block lists, varlen offsets, work partitions and the attention work list.
+#pragma once
+#include <cstdint>
+#include <map>
+#include <utility>
+#include <vector>
+
+#include "common.h"
+
+namespace rt {
+
+// MT19937 with numpy's legacy seeding, masked-rejection bounded integers and
+// Fisher-Yates shuffle (numpy.random.seed / numpy.random.permutation).
+class NumpyLegacyRng {
+ public:
+  void seed(uint32_t s);
+  uint32_t next_u32();
+  uint32_t interval(uint32_t max_inclusive);
+  void shuffle(int32_t* a, int n);
+
+ private:
+  uint32_t key_[624];
+  int pos_ = 624;
+};
+
+// out: [heads][n_blocks-2][r].  Returns RT_ERR_UNSUPPORTED for lengths the
+// validation model itself cannot run (ids beyond the sequence).
+rt_status rand_block_table(uint32_t seed, int heads, int n_blocks, int r, int max_pos, int block,
+                           std::vector<int32_t>& out);
+
+// Key/value block lists of all query blocks of one (sequence, head); `rand`
+// points at this head's [n_blocks-2][r] slice (or null for dense / band).
+void kv_block_lists(const rt_config& cfg, int n_blocks, const int32_t* rand_head,
+                    std::vector<std::vector<int32_t>>& lists);
+
+inline bool uses_random_table(const rt_config& cfg, int n_blocks) {
+  return cfg.pattern == RT_PATTERN_BIGBIRD && n_blocks > 5 + 2 * cfg.num_rand;
+}
+
+struct BlockCsr {
+  std::vector<int32_t> kv_ptr;  // [N+1]
+  std::vector<int32_t> kv_idx;  // [heads][visits]
+  int64_t visits = 0;
+};
+
+// Tables are pure functions of (seed, n_blocks); the cache keeps them across batches.
+using TableCache = std::map<std::pair<uint32_t, int>, std::vector<int32_t>>;
+
+rt_status build_block_csr(const rt_config& cfg, uint32_t layer_seed, const int32_t* lens_tokens, int n_seq,
+                          BlockCsr& out, TableCache* cache);
+
+rt_status validate_lengths(const rt_config& cfg, const int32_t* lens_tokens, int n_seq);
+
+void lpt_partition(const int32_t* cost, int n_qblocks, const int32_t* seq_prefix, int n_seq, int n_parts,
+                   int heads, std::vector<int32_t>& offsets, std::vector<int32_t>& ids);
+
+void binpack_sequences(const double* cost, int n_seq, int n_bins, int32_t* bin_of_seq);
+
+// ---- attention work list ---------------------------------------------------
+struct AttnItem {
+  int32_t q_row0;     // row of query block A in the head-major [T*heads][64] view
+  int32_t q_row1;     // row of query block B (== q_row0 when the item has one block)
+  int32_t kv_row0;    // row of key/value block 0 of this (sequence, head)
+  int32_t entry_off;  // first entry in the entry array
+  int32_t n_entries;
+  int32_t out_tok0;   // first token (packed) of query block A
+  int32_t out_tok1;   // first token of query block B, or -1
+  int32_t head;
+};
+
+struct AttnPlanHost {
+  std::vector<AttnItem> items;     // ordered by CTA
+  std::vector<int32_t> entries;    // (local block id << 2) | mask; mask bit0: block A uses it, bit1: block B
+  std::vector<int32_t> cta_ptr;    // [n_ctas+1]
+  int64_t visits = 0;              // useful (query block, key block) pairs, all heads
+  int total_tokens = 0;
+  int heads = 0;
+};
+
+rt_status build_attn_plan(const rt_config& cfg, const int32_t* lens_tokens, int n_seq, const int32_t* kv_ptr,
+                          const int32_t* kv_idx, int64_t visits_per_head, int n_ctas, AttnPlanHost& out);
+
+}  // namespace rt

@@ -1,0 +1,123 @@
+"""Single CUDA kernels of the encoder on torch CUDA tensors (16-bit), through the C ABI.
+
+torch is used for device memory and streams only; every function launches one
+kernel of this library on the current torch stream and returns its output.
+"""
+import ctypes as C
+
+import torch
+
+from . import capi
+from .capi import check, lib
+
+
+def _dt(t):
+    if t.dtype == torch.bfloat16:
+        return capi.RT_BF16
+    if t.dtype == torch.float16:
+        return capi.RT_F16
+    raise TypeError(f"expected float16 or bfloat16, got {t.dtype}")
+
+
+def _p(t):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise RuntimeError("raptor_t_b200 ops need CUDA tensors (there is no CPU path)")
+    if not t.is_contiguous():
+        raise RuntimeError("raptor_t_b200 ops need contiguous tensors")
+    return C.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def bias_residual_layernorm(x, bias, residual, gamma, beta, eps, out=None):
+    out = x if out is None else out
+    rows, hidden = x.shape
+    check(lib.rt_bias_residual_layernorm(_p(out), _p(x), _p(bias), _p(residual), _p(gamma), _p(beta), rows, hidden,
+                                         float(eps), _dt(x), _stream()))
+    return out
+
+
+def bias_gelu_(x, bias):
+    rows, cols = x.shape
+    check(lib.rt_bias_gelu(_p(x), _p(bias), rows, cols, _dt(x), _stream()))
+    return x
+
+
+def qkv_bias_transpose(qkv, bias, seq_block_prefix_dev, heads, q_scale=0.125, out=None):
+    T = qkv.shape[0]
+    hidden = qkv.shape[1] // 3
+    if out is None:
+        out = tuple(torch.empty(T, hidden, dtype=qkv.dtype, device=qkv.device) for _ in range(3))
+    q, k, v = out
+    check(lib.rt_qkv_bias_transpose(_p(qkv), _p(bias), _p(q), _p(k), _p(v), _p(seq_block_prefix_dev),
+                                    seq_block_prefix_dev.numel() - 1, T // 64, heads, float(q_scale), _dt(qkv),
+                                    _stream()))
+    return q, k, v
+
+
+def embeddings(ids, pos_ids, type_ids, word, pos, typ, gamma, beta, eps, dtype, out=None):
+    T, hidden = ids.numel(), word.shape[1]
+    if out is None:
+        out = torch.empty(T, hidden, dtype=dtype, device=ids.device)
+    check(lib.rt_embeddings(_p(out), _p(ids), _p(pos_ids), _p(type_ids), _p(word), _p(pos), _p(typ), _p(gamma),
+                            _p(beta), T, hidden, float(eps), _dt(out), _stream()))
+    return out
+
+
+def gemm(a, w, bias=None, epilogue=capi.RT_EPI_NONE, out=None):
+    """out[M,N] = a[M,K] @ w[N,K]^T (+bias, +GELU); w is [out_features, in_features]."""
+    M, K = a.shape
+    N = w.shape[0]
+    if out is None:
+        out = torch.empty(M, N, dtype=a.dtype, device=a.device)
+    check(lib.rt_gemm(_p(out), _p(a), _p(w), _p(bias), M, N, K, epilogue, _dt(a), _stream()))
+    return out
+
+
+class AttentionPlan:
+    """Device work list for rt_sparse_attention built from a CSR block table."""
+
+    def __init__(self, cfg, lens_tokens, kv_ptr, kv_idx, n_ctas=0):
+        import numpy as np
+        lens = np.ascontiguousarray(lens_tokens, dtype=np.int32)
+        kv_ptr = np.ascontiguousarray(kv_ptr, dtype=np.int32)
+        kv_idx = np.ascontiguousarray(kv_idx, dtype=np.int32)
+        self._h = C.c_void_p()
+        i32p = C.POINTER(C.c_int32)
+        check(lib.rt_attn_plan_create(C.byref(cfg), lens.ctypes.data_as(i32p), len(lens), kv_ptr.ctypes.data_as(i32p),
+                                      kv_idx.ctypes.data_as(i32p), n_ctas, _stream(), C.byref(self._h)))
+        e, v, it = C.c_int64(), C.c_int64(), C.c_int32()
+        check(lib.rt_attn_plan_stats(self._h, C.byref(e), C.byref(v), C.byref(it)))
+        self.entries, self.visits, self.items = int(e.value), int(v.value), int(it.value)
+
+    @property
+    def handle(self):
+        return self._h
+
+    def close(self):
+        if self._h:
+            lib.rt_attn_plan_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def sparse_attention(q, k, v, plan, scale=1.0, out=None):
+    """q,k,v head-major per sequence ([T, hidden] storage); returns token-major context [T, hidden]."""
+    if out is None:
+        out = torch.empty_like(q)
+    check(lib.rt_sparse_attention(_p(out), _p(q), _p(k), _p(v), plan.handle, float(scale), _dt(q), _stream()))
+    return out
+
+
+def check_device():
+    """Synchronise and raise if any kernel gave up on a bounded device-side wait."""
+    check(lib.rt_check_device())
