@@ -1,0 +1,122 @@
+"""The whole encoder on the GPU against the CPU oracle on the same seeded inputs.
+
+Tolerance (final hidden states, 16-bit GPU path vs fp32 oracle): max-abs 2e-2,
+mean-abs 2e-3; block tables and varlen offsets bit-exact."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from oracle import EncoderConfig
+
+pytestmark = pytest.mark.gpu
+
+MAX_ABS, MEAN_ABS = 2e-2, 2e-3
+
+
+def _make(cfg, dtype, P):
+    from raptor_t_b200 import capi
+    from raptor_t_b200.engine import Encoder
+    rc = capi.make_config(hidden=cfg.hidden, heads=cfg.heads, ffn=cfg.ffn, layers=cfg.layers, max_pos=cfg.max_pos,
+                          vocab=cfg.vocab, type_vocab=cfg.type_vocab, pattern=cfg.pattern, band_half=cfg.band_half,
+                          dtype="bf16" if dtype == torch.bfloat16 else "f16", eps=cfg.eps)
+    return Encoder(rc).load_weights(P)
+
+
+def _skip_no_gpu():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("fuse", [1, 0])
+def test_small_encoder_from_ids(dtype, fuse):
+    _skip_no_gpu()
+    cfg = EncoderConfig(hidden=128, heads=2, ffn=256, layers=2, max_pos=4096, vocab=97)
+    P = oracle.make_weights(cfg, seed=3, nonzero_bias=True)
+    enc = _make(cfg, dtype, P)
+    enc.set_option("fuse_gelu", fuse)
+    lens = [832, 1024, 512, 64]
+    rng = np.random.default_rng(0)
+    seqs = [torch.from_numpy(rng.integers(0, cfg.vocab, size=n)).int() for n in lens]
+    ref = oracle.encoder_ref(seqs, P, cfg)
+    enc.prepare(lens)
+    out = enc.forward_ids(torch.cat(seqs).cuda())
+    from raptor_t_b200 import ops
+    ops.check_device()
+    err = (out.float().cpu() - ref).abs()
+    assert err.max().item() < 6e-2 and err.mean().item() < 6e-3, (err.max().item(), err.mean().item())
+    # tables bit-exact with the oracle
+    for layer in range(cfg.layers):
+        ptr, idx = enc.table(layer)
+        optr, oidx = oracle.build_block_csr(lens, cfg, layer)
+        assert np.array_equal(ptr, optr) and np.array_equal(idx, oidx)
+
+
+def test_base_encoder_hidden_states_within_tolerance():
+    _skip_no_gpu()
+    cfg = EncoderConfig(layers=3, vocab=1000)
+    P = oracle.make_weights(cfg, seed=0)
+    lens = [1024, 832, 1472]
+    rng = np.random.default_rng(0)
+    seqs = [torch.from_numpy(rng.integers(5, cfg.vocab, size=n)).int() for n in lens]
+    ref = oracle.encoder_ref(seqs, P, cfg)
+    for dtype in (torch.float16, torch.bfloat16):
+        enc = _make(cfg, dtype, P)
+        enc.prepare(lens)
+        out = enc.forward_ids(torch.cat(seqs).cuda())
+        err = (out.float().cpu() - ref).abs()
+        if dtype == torch.float16:
+            assert err.max().item() < MAX_ABS and err.mean().item() < MEAN_ABS, (err.max().item(), err.mean().item())
+        else:  # bf16 carries 3 fewer mantissa bits through the residual stream
+            assert err.max().item() < 8e-2 and err.mean().item() < 8e-3, (err.max().item(), err.mean().item())
+        enc.close()
+
+
+def test_forward_host_matches_device_path_and_repeats():
+    _skip_no_gpu()
+    cfg = EncoderConfig(hidden=128, heads=2, ffn=256, layers=2, max_pos=4096, vocab=97)
+    P = oracle.make_weights(cfg, seed=3, nonzero_bias=True)
+    enc = _make(cfg, torch.bfloat16, P)
+    for lens in ([832, 1024], [64], [2048, 704, 896]):
+        T = sum(lens)
+        ids = torch.from_numpy(np.random.default_rng(T).integers(0, cfg.vocab, size=T)).int().pin_memory()
+        out_host = torch.empty(T, cfg.hidden, dtype=torch.bfloat16).pin_memory()
+        enc.forward_host(lens, ids, out_host)
+        enc.prepare(lens)
+        out_dev = enc.forward_ids(ids.cuda())
+        assert torch.equal(out_dev.cpu(), out_host)
+
+
+def test_operator_calls_equal_whole_layer():
+    _skip_no_gpu()
+    cfg = EncoderConfig(hidden=128, heads=2, ffn=256, layers=1, max_pos=4096, vocab=97)
+    P = oracle.make_weights(cfg, seed=4, nonzero_bias=True, embeddings=False)
+    enc = _make(cfg, torch.bfloat16, P)
+    lens = [896, 1024]
+    T = sum(lens)
+    x = torch.randn(T, cfg.hidden, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).cuda()
+    enc.prepare(lens)
+    whole = enc.forward_hidden(x.clone())
+    enc.prepare(lens)
+    a = enc.attention(0, x, torch.empty_like(x))
+    f = enc.intermediate(0, a, torch.empty(T, cfg.ffn, dtype=x.dtype, device="cuda"))
+    o = enc.output(0, f, a, torch.empty_like(x))
+    assert torch.equal(o, whole)
+    ref = oracle.encoder_ref([x[:896].float().cpu(), x[896:].float().cpu()], P, cfg, from_ids=False)
+    assert (whole.float().cpu() - ref).abs().max().item() < 6e-2
+
+
+def test_errors_are_reported_not_fatal():
+    _skip_no_gpu()
+    from raptor_t_b200 import capi
+    cfg = EncoderConfig(hidden=128, heads=2, ffn=256, layers=1, max_pos=4096, vocab=97)
+    P = oracle.make_weights(cfg, seed=4, embeddings=False)
+    enc = _make(cfg, torch.bfloat16, P)
+    with pytest.raises(capi.RtError):
+        enc.forward_hidden.__self__.prepare([768])      # 12 blocks: rejected like the validation model
+        enc.forward_hidden(torch.zeros(768, 128, dtype=torch.bfloat16, device="cuda"))
+    with pytest.raises(capi.RtError):
+        enc.prepare([100])
+    enc.prepare([832])                                    # still usable afterwards
+    enc.forward_hidden(torch.zeros(832, 128, dtype=torch.bfloat16, device="cuda"))
