@@ -67,31 +67,24 @@ __device__ __forceinline__ float warp_sum(float v) {
 // ---------------------------------------------------------------------------
 // residual + bias + LayerNorm: one warp per row, NV 128-bit vectors per lane.
 // Two-pass statistics on the register copy (mean, then sum of squared
-// deviations), fp32 throughout.  Warps walk rows with a grid stride so that
-// bias / gamma / beta are fetched once per warp.
+// deviations), fp32 throughout.  Warps walk rows with a grid stride; bias, gamma
+// and beta are re-read per row from L1 so that the kernel keeps few registers
+// and many warps (loads in flight) per SM.
 // ---------------------------------------------------------------------------
 template <typename T, int NV>
-__global__ void __launch_bounds__(256) layernorm_kernel(T* __restrict__ out, const T* __restrict__ x,
-                                                        const T* __restrict__ bias, const T* __restrict__ residual,
-                                                        const T* __restrict__ gamma, const T* __restrict__ beta,
-                                                        int rows, int hidden, float eps) {
+__global__ void __launch_bounds__(256, (NV <= 4 ? 3 : 2))
+layernorm_kernel(T* __restrict__ out, const T* __restrict__ x, const T* __restrict__ bias,
+                 const T* __restrict__ residual, const T* __restrict__ gamma, const T* __restrict__ beta, int rows,
+                 int hidden, float eps) {
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
   const int warp = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
   const int total_warps = gridDim.x * warps_per_block;
   const int vecs = hidden >> 3;
   const float inv_h = 1.0f / static_cast<float>(hidden);
-
-  uint4 g[NV], b[NV], bi[NV];
-#pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    const int c = lane + 32 * i;
-    if (c < vecs) {
-      g[i] = reinterpret_cast<const uint4*>(gamma)[c];
-      b[i] = reinterpret_cast<const uint4*>(beta)[c];
-      bi[i] = bias ? reinterpret_cast<const uint4*>(bias)[c] : make_uint4(0, 0, 0, 0);
-    }
-  }
+  const uint4* gv = reinterpret_cast<const uint4*>(gamma);
+  const uint4* bv = reinterpret_cast<const uint4*>(beta);
+  const uint4* biv = reinterpret_cast<const uint4*>(bias);
 
   for (int row = warp; row < rows; row += total_warps) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * hidden);
@@ -111,13 +104,18 @@ __global__ void __launch_bounds__(256) layernorm_kernel(T* __restrict__ out, con
     for (int i = 0; i < NV; ++i) {
       const int c = lane + 32 * i;
       if (c < vecs) {
-        float a[8], r[8], bb[8];
+        float a[8], r[8];
         Vec8<T>::unpack(xv[i], a);
         Vec8<T>::unpack(rv[i], r);
-        Vec8<T>::unpack(bi[i], bb);
+        if (biv) {
+          float bb[8];
+          Vec8<T>::unpack(__ldg(biv + c), bb);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) a[k] += bb[k];
+        }
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          v[i][k] = a[k] + bb[k] + r[k];
+          v[i][k] = a[k] + r[k];
           sum += v[i][k];
         }
       } else {
@@ -145,8 +143,8 @@ __global__ void __launch_bounds__(256) layernorm_kernel(T* __restrict__ out, con
       const int c = lane + 32 * i;
       if (c < vecs) {
         float gg[8], be[8], o[8];
-        Vec8<T>::unpack(g[i], gg);
-        Vec8<T>::unpack(b[i], be);
+        Vec8<T>::unpack(__ldg(gv + c), gg);
+        Vec8<T>::unpack(__ldg(bv + c), be);
 #pragma unroll
         for (int k = 0; k < 8; ++k) o[k] = (v[i][k] - mean) * rstd * gg[k] + be[k];
         orow[c] = Vec8<T>::pack(o);
@@ -340,7 +338,7 @@ static rt_status layernorm_launch(void* out, const void* x, const void* bias, co
                                   const void* beta, int rows, int hidden, float eps, cudaStream_t st) {
   const int nv = (hidden / 8 + 31) / 32;
   const int threads = 256, wpb = threads / 32;
-  int blocks = std::min((rows + wpb - 1) / wpb, sm_count() * 8);
+  int blocks = std::min((rows + wpb - 1) / wpb, sm_count() * 16);
   if (blocks < 1) blocks = 1;
 #define RT_LN_CASE(NV)                                                                                           \
   case NV:                                                                                                       \
