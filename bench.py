@@ -251,7 +251,7 @@ def run_gpu(args, w):
     e2e_value = T_total / (e2e_ms_per_step * 1e-3)
     stats = enc.plan_stats(0)
     visits_local = stats["visits"] // w["heads"]
-    meta_bytes = w["layers"] * (stats["items"] * 32 + stats["entries"] * 4 + 149 * 4) + (len(lens) + 1) * 4
+    meta_bytes = w["layers"] * (stats["items"] * 32 + stats["entries"] * 4 + 297 * 4) + (len(lens) + 1) * 4
     h2d = T_local * 4 + meta_bytes
     d2h = T_local * w["hidden"] * 2
 

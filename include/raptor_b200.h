@@ -140,6 +140,17 @@ rt_status rt_attn_plan_destroy(rt_attn_plan* plan);
 rt_status rt_attn_plan_stats(const rt_attn_plan* plan, int64_t* entries_out, int64_t* visits_out,
                              int32_t* items_out);
 
+/* The same work list built on the host only (no GPU; for validation and tooling).
+ * use_templates = 1 takes the cached per-sequence template path the encoder object uses.
+ * items_out: 8 int32 per item {q_row0, q_row1, kv_row0, entry_off, n_entries, out_tok0, out_tok1, head};
+ * entries_out: (sequence-local block id << 2) | mask (bit 0: first query block, bit 1: second);
+ * cta_ptr_out [n_ctas+1].  Pass items_out = NULL to query the sizes.  No reference counterpart
+ * (the reference partitions single query blocks, python/util.py:11-34). */
+rt_status rt_attn_plan_build_host(const rt_config* cfg, uint32_t layer_seed, const int32_t* lens_tokens, int n_seq,
+                                  int n_ctas, int use_templates, int32_t* items_out, int64_t items_cap,
+                                  int32_t* entries_out, int64_t entries_cap, int32_t* cta_ptr_out,
+                                  int64_t* n_items, int64_t* n_entries, int64_t* visits);
+
 /* ctx[token][head*64 + d] = softmax(scale * q k_listed^T) v_listed, online softmax, per work item.
  * q/k/v in the head-major layout of rt_qkv_bias_transpose; ctx_dev is token-major [T][heads*64].
  * layers/kernels/sparse_attention.cu:2953-3228 (sparse_attention_lastest / test_gemm_1). */
@@ -202,6 +213,15 @@ rt_status rt_encoder_get_scratch(rt_encoder* enc, const char* name, void** ptr_d
 rt_status rt_encoder_get_timing(rt_encoder* enc, const char* key, float* ms_out);
 rt_status rt_encoder_enable_timing(rt_encoder* enc, int on);
 rt_status rt_encoder_kernel_launches(rt_encoder* enc, int64_t* launches_out);
+/* options: "fuse_gelu" (1: bias+GELU in the FFN-up GEMM epilogue, 0: separate rt_bias_gelu kernel). */
+rt_status rt_encoder_set_option(rt_encoder* enc, const char* name, int value);
+/* work-list statistics of one layer of the prepared batch */
+rt_status rt_encoder_plan_stats(rt_encoder* enc, int layer, int64_t* entries_out, int64_t* visits_out,
+                                int32_t* items_out);
+/* Synchronises the device and reports (then clears) a kernel that gave up on a bounded wait. */
+rt_status rt_check_device(void);
+/* Kernel launches made by this library in this process so far. */
+int64_t rt_kernel_launches(void);
 
 #ifdef __cplusplus
 }

@@ -10,6 +10,4 @@ Layout:
   engine      whole-encoder object (one C call per forward)
   parallel    whole-sequence partitioning across GPUs + output gather
 """
-from . import capi, metadata  # noqa: F401
-
-__all__ = ["capi", "metadata"]
+__all__ = ["capi", "metadata", "ops", "engine", "raptor_t", "modeling_bert", "parallel", "weights", "build"]

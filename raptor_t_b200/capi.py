@@ -31,9 +31,8 @@ class RtError(RuntimeError):
 
 
 def _load():
-    path = _build.LIB
-    if not os.path.exists(path) or os.environ.get("RAPTOR_B200_REBUILD"):
-        path = _build.build()
+    # build() is a no-op when the library is newer than every source file
+    path = _build.build(force=bool(os.environ.get("RAPTOR_B200_REBUILD")))
     return C.CDLL(path)
 
 
@@ -60,6 +59,8 @@ _SIGS = {
     "rt_gemm": (C.c_int, [_vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp]),
     "rt_attn_plan_create": (C.c_int, [_cfgp, _i32p, C.c_int, _i32p, _i32p, C.c_int, _vp, C.POINTER(_vp)]),
     "rt_attn_plan_destroy": (C.c_int, [_vp]),
+    "rt_attn_plan_build_host": (C.c_int, [_cfgp, C.c_uint32, _i32p, C.c_int, C.c_int, C.c_int, _i32p, C.c_int64, _i32p,
+                                          C.c_int64, _i32p, _i64p, _i64p, _i64p]),
     "rt_attn_plan_stats": (C.c_int, [_vp, _i64p, _i64p, _i32p]),
     "rt_sparse_attention": (C.c_int, [_vp, _vp, _vp, _vp, _vp, C.c_float, C.c_int, _vp]),
     "rt_encoder_create": (C.c_int, [_cfgp, C.POINTER(_vp)]),

@@ -13,9 +13,16 @@
 //            PV = P V (P read from TMEM, V MN-major in shared memory) into one of
 //            two TMEM result buffers.  S of entry j+1 is issued before PV of entry j;
 //   warps 0-3  softmax: thread r owns tile row r.  It pulls its score row out of
-//            TMEM, keeps the running max / sum in fp32 (base-2 exponentials), writes
-//            the 16-bit probabilities back to TMEM for the PV MMA, then folds the
-//            previous entry's PV result into its fp32 output row held in registers.
+//            TMEM, keeps the running max / sum in fp32 (base-2 exponentials) and
+//            writes the 16-bit probabilities back to TMEM for the PV MMA.  The
+//            output tile accumulates in TMEM across the whole list (the PV MMAs
+//            add into it); it is rescaled only when a row's max has grown by more
+//            than 2^8 since the last rescale ("lazy" rescaling: probabilities are
+//            then at most 256, well inside 16-bit range), and read once per item
+//            for the final division by the row sum.
+//
+// Two CTAs share an SM (256 TMEM columns and ~97 KB of shared memory each), so one
+// CTA's softmax latency hides behind the other's.
 //
 // Output rows go token-major [T][heads*64].  Counterpart of
 // layers/kernels/sparse_attention.cu:2953-3228; the math follows the reference's
@@ -43,10 +50,11 @@ constexpr int kThreads = 192;
 constexpr int kStages = 4;               // K/V ring depth
 constexpr int kTileBytes = 64 * 64 * 2;  // one 64 x 64 16-bit block
 constexpr int kQBytes = 2 * kTileBytes;
-constexpr int kTmemCols = 512;
+constexpr int kTmemCols = 256;
 constexpr int kColS = 0;     // 2 x 64 fp32 score columns
 constexpr int kColP = 128;   // 2 x 32 columns of packed 16-bit probabilities
-constexpr int kColPV = 192;  // 2 x 64 fp32 result columns
+constexpr int kColO = 192;   // 64 fp32 output columns, accumulated over the item's list
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 struct Smem {
   uint8_t q[2][kQBytes];
@@ -54,7 +62,7 @@ struct Smem {
   uint8_t v[kStages][kTileBytes];
   uint64_t q_full[2], q_empty[2];
   uint64_t k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
-  uint64_t s_full[2], s_free[2], p_full[2], pv_full[2], pv_free[2];
+  uint64_t s_full[2], s_free[2], p_full[2], pv_done[2], o_free;
   uint32_t tmem_slot;
   int abort_flag;
 };
@@ -78,7 +86,7 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 }
 
 template <bool BF16>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 2)
 sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, uint16_t* __restrict__ ctx,
                         const AttnItem* __restrict__ items, const int32_t* __restrict__ entries,
@@ -95,9 +103,9 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       mbar_init(&sm.s_full[i], 1);
       mbar_init(&sm.s_free[i], 128);
       mbar_init(&sm.p_full[i], 128);
-      mbar_init(&sm.pv_full[i], 1);
-      mbar_init(&sm.pv_free[i], 128);
+      mbar_init(&sm.pv_done[i], 1);
     }
+    mbar_init(&sm.o_free, 128);
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&sm.k_full[s], 1);
       mbar_init(&sm.k_empty[s], 1);
@@ -196,25 +204,30 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         }
         return true;
       };
+      uint32_t pv_itn = 0;
       auto issue_pv = [&]() -> bool {
         const int b = pv_g & 1;
         const uint32_t u = pv_g >> 1;
         const int st = pv_g % kStages;
         const uint32_t ph = (pv_g / kStages) & 1;
         if (!mbar_wait(&sm.v_full[st], ph, ab, 214)) return false;
-        if (!mbar_wait(&sm.pv_free[b], (u & 1) ^ 1, ab, 215)) return false;
+        if (pv_j == 0) {
+          // the output tile is overwritten: the softmax warps must have read the previous item's result
+          if (!mbar_wait(&sm.o_free, (pv_itn & 1) ^ 1, ab, 215)) return false;
+        }
         if (!mbar_wait(&sm.p_full[b], u & 1, ab, 216)) return false;
         tc_fence_after_sync();
         const uint64_t dv = make_smem_desc_sw128(smem_u32(sm.v[st]));
-        const uint32_t d = tmem_base + kColPV + b * 64;
+        const uint32_t d = tmem_base + kColO;
         const uint32_t a = tmem_base + kColP + b * 32;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) mma_ts(d, a + k * 8, dv + (k * 2048 >> 4), idesc_pv, k ? 1u : 0u);
+        for (int k = 0; k < 4; ++k) mma_ts(d, a + k * 8, dv + (k * 2048 >> 4), idesc_pv, (pv_j | k) ? 1u : 0u);
         tc_commit(&sm.v_empty[st]);
-        tc_commit(&sm.pv_full[b]);
+        tc_commit(&sm.pv_done[b]);
         ++pv_g;
         if (++pv_j == pv_n) {
           ++pv_item;
+          ++pv_itn;
           pv_j = 0;
           skip_empty(pv_item, pv_n);
         }
@@ -232,101 +245,130 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const int row = warp * 32 + lane;  // tile row == TMEM lane
     const int half = row >> 6;         // 0: query block A, 1: query block B
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-    uint32_t g = 0;
+    uint32_t g = 0, itn = 0;
     bool ok = true;
     for (int it = item_begin; it < item_end && ok; ++it) {
       const AttnItem item = items[it];
       const int n = item.n_entries;
       if (n == 0) continue;
-      float o[64];
-#pragma unroll
-      for (int i = 0; i < 64; ++i) o[i] = 0.f;
-      float m = -INFINITY, l = 0.f;
-      bool prev_active = false;
-      for (int j = 0; j <= n && ok; ++j) {
+      float m_ref = -INFINITY;  // max the stored probabilities / output are relative to (log2 units)
+      float l = 0.f;
+      for (int j = 0; j < n; ++j) {
+        const uint32_t gj = g + j;
+        const int b = gj & 1;
+        const uint32_t u = gj >> 1;
+        const bool active = ((entries[item.entry_off + j] >> half) & 1) != 0;
+        if (!mbar_wait(&sm.s_full[b], u & 1, ab, 221)) { ok = false; break; }
+        tc_fence_after_sync();
+        uint32_t s[64];
+        if (active) {
+          tmem_ld32(lane_base + kColS + b * 64, s);
+          tmem_ld32(lane_base + kColS + b * 64 + 32, s + 32);
+          tc_wait_ld();
+        }
+        tc_fence_before_sync();
+        mbar_arrive(&sm.s_free[b]);
         float alpha = 1.f;
-        bool active = false;
-        if (j < n) {
-          const uint32_t gj = g + j;
-          const int b = gj & 1;
-          const uint32_t u = gj >> 1;
-          active = ((entries[item.entry_off + j] >> half) & 1) != 0;
-          if (!mbar_wait(&sm.s_full[b], u & 1, ab, 221)) { ok = false; break; }
-          tc_fence_after_sync();
-          uint32_t p[32];
-          if (active) {
-            uint32_t s[64];
-            tmem_ld32(lane_base + kColS + b * 64, s);
-            tmem_ld32(lane_base + kColS + b * 64 + 32, s + 32);
-            tc_wait_ld();
-            tc_fence_before_sync();
-            mbar_arrive(&sm.s_free[b]);
-            float mx = __uint_as_float(s[0]);
+        bool fix = false;
+        if (active) {
+          float mx0 = __uint_as_float(s[0]), mx1 = __uint_as_float(s[1]);
+          float mx2 = __uint_as_float(s[2]), mx3 = __uint_as_float(s[3]);
 #pragma unroll
-            for (int i = 1; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(s[i]));
-            const float m_new = fmaxf(m, mx * scale_log2);
-            alpha = ex2(m - m_new);
-            float sum = 0.f;
+          for (int i = 4; i < 64; i += 4) {
+            mx0 = fmaxf(mx0, __uint_as_float(s[i]));
+            mx1 = fmaxf(mx1, __uint_as_float(s[i + 1]));
+            mx2 = fmaxf(mx2, __uint_as_float(s[i + 2]));
+            mx3 = fmaxf(mx3, __uint_as_float(s[i + 3]));
+          }
+          const float m_new = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;
+          if (m_ref == -INFINITY) {
+            m_ref = m_new;  // nothing accumulated for this row yet (its output columns are still zero)
+          } else if (m_new > m_ref + kRescaleThreshold) {
+            alpha = ex2(m_ref - m_new);
+            m_ref = m_new;
+            fix = true;
+          }
+        }
+        // the probability buffer was last read by the PV MMA two entries back
+        if (gj >= 2) {
+          if (!mbar_wait(&sm.pv_done[b], ((gj - 2) >> 1) & 1, ab, 222)) { ok = false; break; }
+        }
+        if (__any_sync(0xffffffffu, fix)) {
+          // rescale this warp's rows of the output tile; every PV MMA issued so far must be done
+          if (j > 0) {
+            if (!mbar_wait(&sm.pv_done[b ^ 1], ((gj - 1) >> 1) & 1, ab, 223)) { ok = false; break; }
+            tc_fence_after_sync();
+#pragma unroll 1
+            for (int hc = 0; hc < 2; ++hc) {
+              uint32_t o[32];
+              tmem_ld32(lane_base + kColO + hc * 32, o);
+              tc_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const float p0 = ex2(fmaf(__uint_as_float(s[2 * i]), scale_log2, -m_new));
-              const float p1 = ex2(fmaf(__uint_as_float(s[2 * i + 1]), scale_log2, -m_new));
-              sum += p0 + p1;
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              tmem_st32(lane_base + kColO + hc * 32, o);
+            }
+          }
+          l *= alpha;
+        }
+        if (active) {
+          float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+          for (int hc = 0; hc < 2; ++hc) {
+            uint32_t p[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float p0 = ex2(fmaf(__uint_as_float(s[32 * hc + 2 * i]), scale_log2, -m_ref));
+              const float p1 = ex2(fmaf(__uint_as_float(s[32 * hc + 2 * i + 1]), scale_log2, -m_ref));
+              sum0 += p0;
+              sum1 += p1;
               p[i] = pack2<BF16>(p0, p1);
             }
-            l = l * alpha + sum;
-            m = m_new;
-          } else {
-            tc_fence_before_sync();
-            mbar_arrive(&sm.s_free[b]);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) p[i] = 0u;
+            tmem_st16(lane_base + kColP + b * 32 + hc * 16, p);
           }
-          tmem_st32(lane_base + kColP + b * 32, p);
-          tc_wait_st();
-          tc_fence_before_sync();
-          mbar_arrive(&sm.p_full[b]);
-        }
-        if (j > 0) {
-          const uint32_t gp = g + j - 1;
-          const int bp = gp & 1;
-          const uint32_t up = gp >> 1;
-          if (!mbar_wait(&sm.pv_full[bp], up & 1, ab, 222)) { ok = false; break; }
-          tc_fence_after_sync();
-          if (prev_active) {
-            uint32_t r[64];
-            tmem_ld32(lane_base + kColPV + bp * 64, r);
-            tmem_ld32(lane_base + kColPV + bp * 64 + 32, r + 32);
-            tc_wait_ld();
+          l += sum0 + sum1;
+        } else {
+          uint32_t p[16];
 #pragma unroll
-            for (int i = 0; i < 64; ++i) o[i] += __uint_as_float(r[i]);
-          }
-          tc_fence_before_sync();
-          mbar_arrive(&sm.pv_free[bp]);
+          for (int i = 0; i < 16; ++i) p[i] = 0u;
+          tmem_st16(lane_base + kColP + b * 32, p);
+          tmem_st16(lane_base + kColP + b * 32 + 16, p);
         }
-        if (alpha != 1.f) {
-#pragma unroll
-          for (int i = 0; i < 64; ++i) o[i] *= alpha;
-        }
-        prev_active = active;
+        tc_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(&sm.p_full[b]);
       }
-      g += n;
       if (!ok) break;
+      g += n;
+      // final: the last PV MMA of the item completes the output tile
+      {
+        const uint32_t gl = g - 1;
+        if (!mbar_wait(&sm.pv_done[gl & 1], (gl >> 1) & 1, ab, 224)) { ok = false; break; }
+        tc_fence_after_sync();
+      }
       const int tok0 = half == 0 ? item.out_tok0 : item.out_tok1;
+      uint32_t o[64];
+      if (tok0 >= 0) {
+        tmem_ld32(lane_base + kColO, o);
+        tmem_ld32(lane_base + kColO + 32, o + 32);
+        tc_wait_ld();
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&sm.o_free);
+      ++itn;
       if (tok0 >= 0) {
         const float inv = 1.0f / l;
-        uint4* dst = reinterpret_cast<uint4*>(ctx + static_cast<size_t>(tok0 + (row & 63)) * hidden + item.head * 64);
+        uint16_t* dst = ctx + static_cast<size_t>(tok0 + (row & 63)) * hidden + item.head * 64;
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          uint4 v;
-          v.x = pack2<BF16>(o[8 * q + 0] * inv, o[8 * q + 1] * inv);
-          v.y = pack2<BF16>(o[8 * q + 2] * inv, o[8 * q + 3] * inv);
-          v.z = pack2<BF16>(o[8 * q + 4] * inv, o[8 * q + 5] * inv);
-          v.w = pack2<BF16>(o[8 * q + 6] * inv, o[8 * q + 7] * inv);
-          dst[q] = v;
+        for (int q = 0; q < 4; ++q) {
+          uint32_t w[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e)
+            w[e] = pack2<BF16>(__uint_as_float(o[16 * q + 2 * e]) * inv, __uint_as_float(o[16 * q + 2 * e + 1]) * inv);
+          st_global_v8(dst + 16 * q, w);
         }
       }
     }
+    (void)itn;
   }
 
   tc_fence_before_sync();
@@ -403,6 +445,7 @@ extern "C" rt_status rt_attn_plan_create(const rt_config* cfg, const int32_t* le
     int dev = 0;
     RT_CHECK_CUDA(cudaGetDevice(&dev));
     RT_CHECK_CUDA(cudaDeviceGetAttribute(&n_ctas, cudaDevAttrMultiProcessorCount, dev));
+    n_ctas *= 2;  // two CTAs of the attention kernel are resident per SM
   }
   int nblk = 0;
   for (int s = 0; s < n_seq; ++s) nblk += lens[s] / cfg->block;

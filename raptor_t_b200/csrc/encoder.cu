@@ -111,6 +111,7 @@ using namespace rt;
 struct rt_encoder {
   rt_config cfg{};
   int sm_count = 148;
+  int attn_ctas = 296;  // two resident attention CTAs per SM
   std::vector<LayerWeights> layers;
   DevBuf emb_word, emb_pos, emb_type, emb_g, emb_b;
   bool emb_set = false;
@@ -152,6 +153,8 @@ struct rt_encoder {
   int64_t plan_visits = 0;
   int plan_items = 0;
   TableCache table_cache;
+  TemplateCache template_cache;
+  std::vector<bool> csr_valid;         // host CSR copies are built on demand
 
   cudaStream_t meta_stream = nullptr;
   std::thread worker;
@@ -225,15 +228,28 @@ struct Span {
 };
 
 void worker_main(rt_encoder* e) {
-  // One pass over the layers: CSR table -> work list -> pinned region -> async upload -> event.
+  // One pass over the layers: per-sequence templates (cached across batches) -> batch work
+  // list -> pinned region -> async upload -> event.
   cudaSetDevice(e->device);
   rt_encoder::Slot& slot = *e->cur;
+  std::vector<const SeqTemplate*> tmpl(e->n_seq);
   for (int l = 0; l < e->cfg.layers; ++l) {
-    rt_status s = build_block_csr(e->cfg, e->layers[l].seed, e->lens.data(), e->n_seq, e->csr[l], &e->table_cache);
+    rt_status s = RT_OK;
+    for (int q = 0; q < e->n_seq && s == RT_OK; ++q) {
+      const int L = e->lens[q] / e->cfg.block;
+      // lists that do not depend on a random table are shared by all layers
+      const uint32_t seed = uses_random_table(e->cfg, L) ? e->layers[l].seed : 0xffffffffu;
+      auto key = std::make_pair(seed, L);
+      auto it = e->template_cache.find(key);
+      if (it == e->template_cache.end()) {
+        SeqTemplate t;
+        s = build_seq_template(e->cfg, seed, L, &e->table_cache, t);
+        if (s == RT_OK) it = e->template_cache.emplace(key, std::move(t)).first;
+      }
+      if (s == RT_OK) tmpl[q] = &it->second;
+    }
     AttnPlanHost plan;
-    if (s == RT_OK)
-      s = build_attn_plan(e->cfg, e->lens.data(), e->n_seq, e->csr[l].kv_ptr.data(), e->csr[l].kv_idx.data(),
-                          e->csr[l].visits, e->sm_count, plan);
+    if (s == RT_OK) s = assemble_attn_plan(e->cfg, e->lens.data(), e->n_seq, tmpl.data(), e->attn_ctas, plan);
     if (s == RT_OK) {
       uint8_t* host = slot.meta_pinned + static_cast<size_t>(l) * e->region_bytes;
       uint8_t* dev = static_cast<uint8_t*>(slot.meta_dev.p) + static_cast<size_t>(l) * e->region_bytes;
@@ -248,8 +264,13 @@ void worker_main(rt_encoder* e) {
         std::memcpy(host + e->items_off, plan.items.data(), items_b);
         std::memcpy(host + e->entries_off, plan.entries.data(), entries_b);
         std::memcpy(host + e->cta_off, plan.cta_ptr.data(), cta_b);
-        // one copy covers items..cta_ptr (gaps included); regions are a few hundred KB
-        cudaError_t ce = cudaMemcpyAsync(dev, host, e->region_bytes, cudaMemcpyHostToDevice, e->meta_stream);
+        cudaError_t ce = cudaMemcpyAsync(dev + e->items_off, host + e->items_off, items_b, cudaMemcpyHostToDevice,
+                                         e->meta_stream);
+        if (ce == cudaSuccess)
+          ce = cudaMemcpyAsync(dev + e->entries_off, host + e->entries_off, entries_b, cudaMemcpyHostToDevice,
+                               e->meta_stream);
+        if (ce == cudaSuccess)
+          ce = cudaMemcpyAsync(dev + e->cta_off, host + e->cta_off, cta_b, cudaMemcpyHostToDevice, e->meta_stream);
         if (ce == cudaSuccess) ce = cudaEventRecord(slot.table_ready[l], e->meta_stream);
         if (ce != cudaSuccess) {
           s = RT_ERR_CUDA;
@@ -333,7 +354,7 @@ rt_status run_attention(rt_encoder* e, int l, const void* input, void* output, c
     const uint8_t* dev = static_cast<const uint8_t*>(e->cur->meta_dev.p) + static_cast<size_t>(l) * e->region_bytes;
     RT_TRY(launch_sparse_attention(ctx, q, k, v, reinterpret_cast<const AttnItem*>(dev + e->items_off),
                                    reinterpret_cast<const int32_t*>(dev + e->entries_off),
-                                   reinterpret_cast<const int32_t*>(dev + e->cta_off), e->sm_count, T, c.heads, 1.0f, dt,
+                                   reinterpret_cast<const int32_t*>(dev + e->cta_off), e->attn_ctas, T, c.heads, 1.0f, dt,
                                    st));
   }
   {
@@ -397,9 +418,11 @@ extern "C" rt_status rt_encoder_create(const rt_config* cfg, rt_encoder** out) {
   e->layers.resize(cfg->layers);
   for (int l = 0; l < cfg->layers; ++l) e->layers[l].seed = static_cast<uint32_t>(l);
   e->csr.resize(cfg->layers);
+  e->csr_valid.assign(cfg->layers, false);
   e->plan_entries.assign(cfg->layers, 0);
   cudaGetDevice(&e->device);
   cudaDeviceGetAttribute(&e->sm_count, cudaDevAttrMultiProcessorCount, e->device);
+  e->attn_ctas = 2 * e->sm_count;
   if (cudaStreamCreateWithFlags(&e->meta_stream, cudaStreamNonBlocking) != cudaSuccess) {
     delete e;
     return fail(RT_ERR_CUDA, "encoder_create: cannot create the metadata stream");
@@ -536,7 +559,7 @@ extern "C" rt_status rt_encoder_prepare_batch(rt_encoder* e, const int32_t* lens
   e->items_off = 0;
   e->entries_off = align256(n_items * sizeof(AttnItem));
   e->cta_off = e->entries_off + align256(static_cast<size_t>(visits) * e->cfg.heads * sizeof(int32_t));
-  e->region_bytes = e->cta_off + align256((e->sm_count + 1) * sizeof(int32_t));
+  e->region_bytes = e->cta_off + align256((e->attn_ctas + 1) * sizeof(int32_t));
   const size_t need = e->region_bytes * e->cfg.layers;
   if (need > slot.meta_cap) {
     if (slot.meta_pinned) cudaFreeHost(slot.meta_pinned);
@@ -553,6 +576,7 @@ extern "C" rt_status rt_encoder_prepare_batch(rt_encoder* e, const int32_t* lens
     e->worker_error.clear();
   }
   e->pre_process_ms = 0.0;
+  e->csr_valid.assign(e->cfg.layers, false);
   e->worker = std::thread(worker_main, e);
   e->prepared = true;
   return RT_OK;
@@ -664,6 +688,10 @@ extern "C" rt_status rt_encoder_get_table(rt_encoder* e, int layer, const int32_
   RT_REQUIRE(layer >= 0 && layer < e->cfg.layers, RT_ERR_INVALID, "get_table: layer out of range");
   e->join_worker();
   if (e->worker_status != RT_OK) return fail(e->worker_status, "metadata worker: %s", e->worker_error.c_str());
+  if (!e->csr_valid[layer]) {
+    RT_TRY(build_block_csr(e->cfg, e->layers[layer].seed, e->lens.data(), e->n_seq, e->csr[layer], &e->table_cache));
+    e->csr_valid[layer] = true;
+  }
   if (kv_ptr) *kv_ptr = e->csr[layer].kv_ptr.data();
   if (kv_idx) *kv_idx = e->csr[layer].kv_idx.data();
   if (visits) *visits = e->csr[layer].visits;

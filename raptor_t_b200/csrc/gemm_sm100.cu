@@ -203,9 +203,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           }
         }
         if (row < M) {
-          uint4* dst = reinterpret_cast<uint4*>(C + static_cast<size_t>(row) * N + n0 + c * 32);
-#pragma unroll
-          for (int q = 0; q < 4; ++q) dst[q] = make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+          uint16_t* dst = C + static_cast<size_t>(row) * N + n0 + c * 32;
+          st_global_v8(dst, o);
+          st_global_v8(dst + 16, o + 8);
         }
       }
       tc_fence_before_sync();

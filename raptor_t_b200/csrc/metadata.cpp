@@ -299,55 +299,127 @@ void binpack_sequences(const double* cost, int n_seq, int n_bins, int32_t* bin_o
 // ---------------------------------------------------------------------------
 // attention work list
 // ---------------------------------------------------------------------------
+namespace {
+
+void query_block_pairs(const rt_config& cfg, int L, std::vector<std::pair<int, int>>& pairs) {
+  pairs.clear();
+  if (uses_random_table(cfg, L)) {
+    pairs.emplace_back(0, L - 1);  // identical lists (every block)
+    for (int q = 1; q <= L - 2; q += 2) pairs.emplace_back(q, q + 1 <= L - 2 ? q + 1 : -1);
+  } else if (cfg.pattern == RT_PATTERN_BAND) {
+    pairs.emplace_back(0, -1);
+    for (int q = 1; q < L; q += 2) pairs.emplace_back(q, q + 1 < L ? q + 1 : -1);
+  } else {
+    for (int q = 0; q < L; q += 2) pairs.emplace_back(q, q + 1 < L ? q + 1 : -1);
+  }
+}
+
+// Multiset union of two block lists: an id present in both (per occurrence) gets mask 3,
+// otherwise mask 1 (first list only) or 2 (second list only).  Appends to ent.
+rt_status merge_lists(const int32_t* la, int na, const int32_t* lb, int nb, int L, std::vector<char>& used,
+                      std::vector<int32_t>& ent) {
+  for (int i = 0; i < na; ++i)
+    RT_REQUIRE(la[i] >= 0 && la[i] < L, RT_ERR_INVALID, "block id %d outside sequence of %d blocks", la[i], L);
+  for (int j = 0; j < nb; ++j)
+    RT_REQUIRE(lb[j] >= 0 && lb[j] < L, RT_ERR_INVALID, "block id %d outside sequence of %d blocks", lb[j], L);
+  if (na == nb && std::equal(la, la + na, lb)) {
+    for (int i = 0; i < na; ++i) ent.push_back((la[i] << 2) | 3);
+    return RT_OK;
+  }
+  used.assign(nb, 0);
+  for (int i = 0; i < na; ++i) {
+    int mask = 1;
+    for (int j = 0; j < nb; ++j)
+      if (!used[j] && lb[j] == la[i]) {
+        used[j] = 1;
+        mask = 3;
+        break;
+      }
+    ent.push_back((la[i] << 2) | mask);
+  }
+  for (int j = 0; j < nb; ++j)
+    if (!used[j]) ent.push_back((lb[j] << 2) | 2);
+  return RT_OK;
+}
+
+struct ItemRef {
+  int32_t n_entries;
+  const int32_t* ent;
+  AttnItem it;
+};
+
+void assign_and_emit(std::vector<ItemRef>& refs, int n_ctas, AttnPlanHost& out) {
+  // longest-processing-time assignment of items to CTAs (+2: per-item prologue/epilogue cost)
+  std::vector<int> order(refs.size());
+  std::iota(order.begin(), order.end(), 0);
+  std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return refs[a].n_entries > refs[b].n_entries; });
+  using Entry = std::pair<int64_t, int32_t>;
+  std::priority_queue<Entry, std::vector<Entry>, std::greater<Entry>> heap;
+  for (int c = 0; c < n_ctas; ++c) heap.emplace(0, c);
+  std::vector<int32_t> cta_of(refs.size());
+  std::vector<int32_t> count(n_ctas + 1, 0);
+  size_t total_entries = 0;
+  for (int i : order) {
+    Entry e = heap.top();
+    heap.pop();
+    cta_of[i] = e.second;
+    ++count[e.second + 1];
+    heap.emplace(e.first + refs[i].n_entries + 2, e.second);
+    total_entries += refs[i].n_entries;
+  }
+  out.cta_ptr.assign(n_ctas + 1, 0);
+  for (int c = 0; c < n_ctas; ++c) out.cta_ptr[c + 1] = out.cta_ptr[c] + count[c + 1];
+  std::vector<int32_t> cursor(out.cta_ptr.begin(), out.cta_ptr.end() - 1);
+  out.items.resize(refs.size());
+  std::vector<int32_t> slot_of(refs.size());
+  for (int i : order) slot_of[i] = cursor[cta_of[i]]++;  // descending cost inside each CTA
+  std::vector<int32_t> pos_item(refs.size());
+  for (size_t i = 0; i < refs.size(); ++i) pos_item[slot_of[i]] = static_cast<int32_t>(i);
+  out.entries.resize(total_entries);
+  size_t off = 0;
+  for (size_t sidx = 0; sidx < refs.size(); ++sidx) {
+    const ItemRef& r = refs[pos_item[sidx]];
+    AttnItem it = r.it;
+    it.entry_off = static_cast<int32_t>(off);
+    it.n_entries = r.n_entries;
+    std::copy(r.ent, r.ent + r.n_entries, out.entries.begin() + off);
+    off += r.n_entries;
+    out.items[sidx] = it;
+  }
+}
+
+}  // namespace
+
 rt_status build_attn_plan(const rt_config& cfg, const int32_t* lens, int n_seq, const int32_t* kv_ptr,
                           const int32_t* kv_idx, int64_t visits_per_head, int n_ctas, AttnPlanHost& out) {
   RT_REQUIRE(n_ctas > 0, RT_ERR_INVALID, "attention plan needs at least one CTA");
   const int nh = cfg.heads, B = cfg.block;
-  struct Proto {
+  std::vector<int32_t> pool;  // all merged lists, back to back
+  struct Pending {
     AttnItem it;
-    std::vector<int32_t> ent;
+    size_t off;
+    int32_t n;
   };
-  std::vector<Proto> protos;
+  std::vector<Pending> pend;
   int tok0 = 0, qbase = 0;
   std::vector<std::pair<int, int>> pairs;
   std::vector<char> used;
+  out = AttnPlanHost();
   for (int s = 0; s < n_seq; ++s) {
     const int L = lens[s] / B;
-    pairs.clear();
-    if (uses_random_table(cfg, L)) {
-      pairs.emplace_back(0, L - 1);  // identical lists (every block)
-      for (int q = 1; q <= L - 2; q += 2) pairs.emplace_back(q, q + 1 <= L - 2 ? q + 1 : -1);
-    } else if (cfg.pattern == RT_PATTERN_BAND) {
-      pairs.emplace_back(0, -1);
-      for (int q = 1; q < L; q += 2) pairs.emplace_back(q, q + 1 < L ? q + 1 : -1);
-    } else {
-      for (int q = 0; q < L; q += 2) pairs.emplace_back(q, q + 1 < L ? q + 1 : -1);
-    }
+    query_block_pairs(cfg, L, pairs);
     for (int h = 0; h < nh; ++h) {
       const int32_t* idx = kv_idx + static_cast<size_t>(h) * visits_per_head;
       for (auto& pr : pairs) {
-        Proto p;
         const int qa = pr.first, qb = pr.second;
         const int32_t* la = idx + kv_ptr[qbase + qa];
         const int na = kv_ptr[qbase + qa + 1] - kv_ptr[qbase + qa];
         const int32_t* lb = qb >= 0 ? idx + kv_ptr[qbase + qb] : nullptr;
         const int nb = qb >= 0 ? kv_ptr[qbase + qb + 1] - kv_ptr[qbase + qb] : 0;
-        used.assign(nb, 0);
-        for (int i = 0; i < na; ++i) {
-          RT_REQUIRE(la[i] >= 0 && la[i] < L, RT_ERR_INVALID, "block id %d outside sequence of %d blocks", la[i], L);
-          int mask = 1;
-          for (int j = 0; j < nb; ++j)
-            if (!used[j] && lb[j] == la[i]) {
-              used[j] = 1;
-              mask = 3;
-              break;
-            }
-          p.ent.push_back((la[i] << 2) | mask);
-        }
-        for (int j = 0; j < nb; ++j) {
-          RT_REQUIRE(lb[j] >= 0 && lb[j] < L, RT_ERR_INVALID, "block id %d outside sequence of %d blocks", lb[j], L);
-          if (!used[j]) p.ent.push_back((lb[j] << 2) | 2);
-        }
+        Pending p;
+        p.off = pool.size();
+        RT_TRY(merge_lists(la, na, lb, nb, L, used, pool));
+        p.n = static_cast<int32_t>(pool.size() - p.off);
         const int base_row = tok0 * nh + h * lens[s];
         p.it.kv_row0 = base_row;
         p.it.q_row0 = base_row + qa * B;
@@ -355,42 +427,102 @@ rt_status build_attn_plan(const rt_config& cfg, const int32_t* lens, int n_seq, 
         p.it.out_tok0 = tok0 + qa * B;
         p.it.out_tok1 = qb >= 0 ? tok0 + qb * B : -1;
         p.it.head = h;
-        p.it.n_entries = static_cast<int32_t>(p.ent.size());
+        p.it.n_entries = p.n;
         p.it.entry_off = 0;
         out.visits += na + nb;
-        protos.push_back(std::move(p));
+        pend.push_back(p);
       }
     }
     tok0 += lens[s];
     qbase += L;
   }
-  // longest-processing-time assignment of items to CTAs
-  std::vector<int> order(protos.size());
-  std::iota(order.begin(), order.end(), 0);
-  std::stable_sort(order.begin(), order.end(),
-                   [&](int a, int b) { return protos[a].it.n_entries > protos[b].it.n_entries; });
-  using Entry = std::pair<int64_t, int32_t>;
-  std::priority_queue<Entry, std::vector<Entry>, std::greater<Entry>> heap;
-  for (int c = 0; c < n_ctas; ++c) heap.emplace(0, c);
-  std::vector<std::vector<int>> per_cta(n_ctas);
-  for (int i : order) {
-    Entry e = heap.top();
-    heap.pop();
-    per_cta[e.second].push_back(i);
-    heap.emplace(e.first + protos[i].it.n_entries + 2, e.second);  // +2: per-item prologue/epilogue cost
-  }
-  out.items.clear();
-  out.entries.clear();
-  out.cta_ptr.assign(1, 0);
-  for (int c = 0; c < n_ctas; ++c) {
-    for (int i : per_cta[c]) {
-      AttnItem it = protos[i].it;
-      it.entry_off = static_cast<int32_t>(out.entries.size());
-      out.entries.insert(out.entries.end(), protos[i].ent.begin(), protos[i].ent.end());
-      out.items.push_back(it);
+  std::vector<ItemRef> refs(pend.size());
+  for (size_t i = 0; i < pend.size(); ++i) refs[i] = ItemRef{pend[i].n, pool.data() + pend[i].off, pend[i].it};
+  assign_and_emit(refs, n_ctas, out);
+  out.total_tokens = tok0;
+  out.heads = nh;
+  return RT_OK;
+}
+
+rt_status build_seq_template(const rt_config& cfg, uint32_t seed, int L, TableCache* tables, SeqTemplate& out) {
+  out = SeqTemplate();
+  out.n_blocks = L;
+  const int32_t* table = nullptr;
+  std::vector<int32_t> local;
+  if (uses_random_table(cfg, L)) {
+    auto key = std::make_pair(seed, L);
+    if (tables && tables->count(key)) {
+      table = (*tables)[key].data();
+    } else {
+      RT_TRY(rand_block_table(seed, cfg.heads, L, cfg.num_rand, cfg.max_pos, cfg.block, local));
+      if (tables) {
+        auto it = tables->emplace(key, std::move(local)).first;
+        table = it->second.data();
+      } else {
+        table = local.data();
+      }
     }
-    out.cta_ptr.push_back(static_cast<int32_t>(out.items.size()));
   }
+  std::vector<std::pair<int, int>> pairs;
+  query_block_pairs(cfg, L, pairs);
+  out.n_pairs = static_cast<int>(pairs.size());
+  for (auto& pr : pairs) {
+    out.qa.push_back(pr.first);
+    out.qb.push_back(pr.second);
+  }
+  std::vector<std::vector<int32_t>> lists;
+  std::vector<char> used;
+  out.item_off.push_back(0);
+  for (int h = 0; h < cfg.heads; ++h) {
+    kv_block_lists(cfg, L, table ? table + static_cast<size_t>(h) * (L - 2) * cfg.num_rand : nullptr, lists);
+    for (auto& pr : pairs) {
+      const auto& la = lists[pr.first];
+      static const std::vector<int32_t> kEmpty;
+      const auto& lb = pr.second >= 0 ? lists[pr.second] : kEmpty;
+      RT_TRY(merge_lists(la.data(), static_cast<int>(la.size()), lb.data(), static_cast<int>(lb.size()), L, used,
+                         out.ent));
+      out.item_off.push_back(static_cast<int32_t>(out.ent.size()));
+      out.visits += static_cast<int64_t>(la.size() + lb.size());
+    }
+  }
+  return RT_OK;
+}
+
+rt_status assemble_attn_plan(const rt_config& cfg, const int32_t* lens, int n_seq,
+                             const SeqTemplate* const* templates, int n_ctas, AttnPlanHost& out) {
+  RT_REQUIRE(n_ctas > 0, RT_ERR_INVALID, "attention plan needs at least one CTA");
+  const int nh = cfg.heads, B = cfg.block;
+  out = AttnPlanHost();
+  size_t n_items = 0;
+  for (int s = 0; s < n_seq; ++s) n_items += static_cast<size_t>(templates[s]->n_pairs) * nh;
+  std::vector<ItemRef> refs;
+  refs.reserve(n_items);
+  int tok0 = 0;
+  for (int s = 0; s < n_seq; ++s) {
+    const SeqTemplate& t = *templates[s];
+    RT_REQUIRE(t.n_blocks * B == lens[s], RT_ERR_STATE, "template does not match sequence %d", s);
+    for (int h = 0; h < nh; ++h) {
+      const int base_row = tok0 * nh + h * lens[s];
+      for (int p = 0; p < t.n_pairs; ++p) {
+        const int idx = h * t.n_pairs + p;
+        ItemRef r;
+        r.n_entries = t.item_off[idx + 1] - t.item_off[idx];
+        r.ent = t.ent.data() + t.item_off[idx];
+        r.it.kv_row0 = base_row;
+        r.it.q_row0 = base_row + t.qa[p] * B;
+        r.it.q_row1 = t.qb[p] >= 0 ? base_row + t.qb[p] * B : r.it.q_row0;
+        r.it.out_tok0 = tok0 + t.qa[p] * B;
+        r.it.out_tok1 = t.qb[p] >= 0 ? tok0 + t.qb[p] * B : -1;
+        r.it.head = h;
+        r.it.entry_off = 0;
+        r.it.n_entries = r.n_entries;
+        refs.push_back(r);
+      }
+    }
+    out.visits += t.visits;
+    tok0 += lens[s];
+  }
+  assign_and_emit(refs, n_ctas, out);
   out.total_tokens = tok0;
   out.heads = nh;
   return RT_OK;

@@ -82,4 +82,25 @@ struct AttnPlanHost {
 rt_status build_attn_plan(const rt_config& cfg, const int32_t* lens_tokens, int n_seq, const int32_t* kv_ptr,
                           const int32_t* kv_idx, int64_t visits_per_head, int n_ctas, AttnPlanHost& out);
 
+// Work-list template of ONE sequence of n_blocks blocks under one table seed, all heads:
+// the query-block pairs and their merged, masked key/value lists with sequence-local
+// block ids.  A pure function of (seed, n_blocks), so it is cached across batches; a
+// batch's work list is assembled from the templates of its sequences.
+struct SeqTemplate {
+  int n_blocks = 0;
+  int n_pairs = 0;                  // items per head
+  std::vector<int32_t> qa, qb;      // [n_pairs] query blocks of a pair (qb = -1: single)
+  std::vector<int32_t> item_off;    // [heads * n_pairs + 1] offsets into ent
+  std::vector<int32_t> ent;         // (local block id << 2) | mask
+  int64_t visits = 0;               // useful (query block, key block) pairs, all heads
+};
+using TemplateCache = std::map<std::pair<uint32_t, int>, SeqTemplate>;
+
+rt_status build_seq_template(const rt_config& cfg, uint32_t seed, int n_blocks, TableCache* tables, SeqTemplate& out);
+
+// Assemble the batch work list from per-sequence templates (templates[s] for sequence s)
+// and assign items to CTAs (longest processing time first).
+rt_status assemble_attn_plan(const rt_config& cfg, const int32_t* lens_tokens, int n_seq,
+                             const SeqTemplate* const* templates, int n_ctas, AttnPlanHost& out);
+
 }  // namespace rt

@@ -153,3 +153,50 @@ extern "C" rt_status rt_binpack_sequences(const double* cost, int n_seq, int n_b
   binpack_sequences(cost, n_seq, n_bins, bin_of_seq_host);
   return RT_OK;
 }
+
+// Host-only construction of the attention work list (no GPU): via the CSR table
+// (use_templates = 0) or via the cached per-sequence templates the encoder uses
+// (use_templates = 1).  items_out holds 8 int32 per item in AttnItem field order.
+extern "C" rt_status rt_attn_plan_build_host(const rt_config* cfg, uint32_t layer_seed, const int32_t* lens, int n_seq,
+                                             int n_ctas, int use_templates, int32_t* items_out, int64_t items_cap,
+                                             int32_t* entries_out, int64_t entries_cap, int32_t* cta_ptr_out,
+                                             int64_t* n_items, int64_t* n_entries, int64_t* visits) {
+  RT_TRY(check_cfg(cfg));
+  RT_REQUIRE(n_items && n_entries && visits, RT_ERR_INVALID, "attn_plan_build_host: null counters");
+  RT_TRY(validate_lengths(*cfg, lens, n_seq));
+  AttnPlanHost plan;
+  TableCache tables;
+  if (use_templates) {
+    TemplateCache cache;
+    std::vector<const SeqTemplate*> tmpl(n_seq);
+    for (int q = 0; q < n_seq; ++q) {
+      const int L = lens[q] / cfg->block;
+      const uint32_t seed = uses_random_table(*cfg, L) ? layer_seed : 0xffffffffu;
+      auto key = std::make_pair(seed, L);
+      auto it = cache.find(key);
+      if (it == cache.end()) {
+        SeqTemplate t;
+        RT_TRY(build_seq_template(*cfg, seed, L, &tables, t));
+        it = cache.emplace(key, std::move(t)).first;
+      }
+      tmpl[q] = &it->second;
+    }
+    RT_TRY(assemble_attn_plan(*cfg, lens, n_seq, tmpl.data(), n_ctas, plan));
+  } else {
+    BlockCsr csr;
+    RT_TRY(build_block_csr(*cfg, layer_seed, lens, n_seq, csr, &tables));
+    RT_TRY(build_attn_plan(*cfg, lens, n_seq, csr.kv_ptr.data(), csr.kv_idx.data(), csr.visits, n_ctas, plan));
+  }
+  *n_items = static_cast<int64_t>(plan.items.size());
+  *n_entries = static_cast<int64_t>(plan.entries.size());
+  *visits = plan.visits;
+  if (items_out) {
+    RT_REQUIRE(items_cap >= *n_items && entries_cap >= *n_entries && entries_out && cta_ptr_out, RT_ERR_INVALID,
+               "attn_plan_build_host: output buffers too small");
+    static_assert(sizeof(AttnItem) == 8 * sizeof(int32_t), "AttnItem layout");
+    std::memcpy(items_out, plan.items.data(), plan.items.size() * sizeof(AttnItem));
+    std::memcpy(entries_out, plan.entries.data(), plan.entries.size() * sizeof(int32_t));
+    std::memcpy(cta_ptr_out, plan.cta_ptr.data(), plan.cta_ptr.size() * sizeof(int32_t));
+  }
+  return RT_OK;
+}

@@ -85,3 +85,19 @@ def generate_data_metainfo(seq_lens_tokens, block_size=64, thread_block_limit=16
 def sequence_cost(n_tokens, hidden, ffn, heads, visits_per_head):
     """FLOPs of one sequence in one layer: GEMMs + listed attention blocks."""
     return float(n_tokens) * (8 * hidden * hidden + 4 * hidden * ffn) + float(heads) * 1048576.0 * visits_per_head
+
+
+def attention_plan_host(cfg, layer_seed, lens_tokens, n_ctas, use_templates=True):
+    """Host-only work list: dict(items [n,8], entries [m], cta_ptr [n_ctas+1], visits)."""
+    lens, lp = _i32(lens_tokens)
+    ni, ne, vis = C.c_int64(), C.c_int64(), C.c_int64()
+    i32p = C.POINTER(C.c_int32)
+    check(lib.rt_attn_plan_build_host(C.byref(cfg), int(layer_seed), lp, len(lens), n_ctas, int(use_templates), None, 0,
+                                      None, 0, None, C.byref(ni), C.byref(ne), C.byref(vis)))
+    items = np.zeros((ni.value, 8), dtype=np.int32)
+    entries = np.zeros(ne.value, dtype=np.int32)
+    cta_ptr = np.zeros(n_ctas + 1, dtype=np.int32)
+    check(lib.rt_attn_plan_build_host(C.byref(cfg), int(layer_seed), lp, len(lens), n_ctas, int(use_templates),
+                                      items.ctypes.data_as(i32p), ni.value, entries.ctypes.data_as(i32p), ne.value,
+                                      cta_ptr.ctypes.data_as(i32p), C.byref(ni), C.byref(ne), C.byref(vis)))
+    return {"items": items, "entries": entries, "cta_ptr": cta_ptr, "visits": int(vis.value)}

@@ -108,3 +108,69 @@ def test_binpack_matches_oracle():
             assert sorted(np.nonzero(bins == b)[0].tolist()) == sorted(members)
         loads = [costs[bins == b].sum() for b in range(n)]
         assert max(loads) / (costs.sum() / n) < 1.05
+
+
+@pytest.mark.parametrize("pattern,lens", [("bigbird", [1024, 832, 4096, 512, 704, 1984, 64, 128]),
+                                          ("band", [1280, 64, 512, 2048]), ("bigbird", [960])])
+@pytest.mark.parametrize("use_templates", [0, 1])
+def test_attention_work_list_covers_every_block_list_once(pattern, lens, use_templates):
+    """Every (sequence, head, query block) appears in exactly one work item and the masked
+    entries of that item reproduce its key/value list as a multiset."""
+    from collections import Counter
+    o = EncoderConfig(pattern=pattern)
+    cfg = _cfg(o)
+    layer, n_ctas = 3, 296
+    plan = metadata.attention_plan_host(cfg, layer, lens, n_ctas, use_templates)
+    items, entries, cta_ptr = plan["items"], plan["entries"], plan["cta_ptr"]
+    assert cta_ptr[0] == 0 and cta_ptr[-1] == len(items) and np.all(np.diff(cta_ptr) >= 0)
+    starts = np.concatenate([[0], np.cumsum(lens)])
+    seen = set()
+    visits = 0
+    expected = {}
+    for s, n in enumerate(lens):
+        L = n // 64
+        rand = None
+        if pattern == "bigbird" and L > 11:
+            rand = oracle.rand_block_table(layer, o.heads, L, 3, o.max_pos)
+        for h in range(o.heads):
+            for q, lst in enumerate(oracle.kv_block_lists(L, o, rand, h)):
+                expected[(s, h, q)] = Counter(lst)
+    for q_row0, q_row1, kv_row0, off, n_ent, tok0, tok1, head in items.tolist():
+        s = int(np.searchsorted(starts, tok0, side="right") - 1)
+        n = lens[s]
+        assert kv_row0 == starts[s] * o.heads + head * n
+        qa = (tok0 - starts[s]) // 64
+        assert q_row0 == kv_row0 + qa * 64
+        ent = entries[off:off + n_ent]
+        blocks, masks = ent >> 2, ent & 3
+        assert np.all(masks > 0) and np.all(blocks < n // 64)
+        got_a = Counter(blocks[(masks & 1) != 0].tolist())
+        assert got_a == expected[(s, head, qa)]
+        assert (s, head, qa) not in seen
+        seen.add((s, head, qa))
+        visits += sum(got_a.values())
+        if tok1 >= 0:
+            qb = (tok1 - starts[s]) // 64
+            assert q_row1 == kv_row0 + qb * 64
+            got_b = Counter(blocks[(masks & 2) != 0].tolist())
+            assert got_b == expected[(s, head, qb)]
+            assert (s, head, qb) not in seen
+            seen.add((s, head, qb))
+            visits += sum(got_b.values())
+        else:
+            assert q_row1 == q_row0 and not np.any(masks & 2)
+    assert len(seen) == len(expected) and visits == plan["visits"]
+    # load balance of the longest-processing-time assignment
+    loads = [int(items[cta_ptr[c]:cta_ptr[c + 1], 4].sum()) for c in range(n_ctas)]
+    if len(items) >= 4 * n_ctas:
+        assert max(loads) <= 1.25 * (sum(loads) / n_ctas) + 64
+
+
+def test_template_and_csr_work_lists_agree():
+    o = EncoderConfig()
+    cfg = _cfg(o)
+    lens = [1024, 832, 4096, 704]
+    a = metadata.attention_plan_host(cfg, 1, lens, 296, 0)
+    b = metadata.attention_plan_host(cfg, 1, lens, 296, 1)
+    assert np.array_equal(a["items"], b["items"]) and np.array_equal(a["entries"], b["entries"])
+    assert np.array_equal(a["cta_ptr"], b["cta_ptr"]) and a["visits"] == b["visits"]

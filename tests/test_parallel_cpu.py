@@ -1,0 +1,51 @@
+"""Multi-rank host logic on CPU: whole-sequence partitioning and the output gather
+(gloo, world size 2)."""
+import os
+import socket
+
+import numpy as np
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from raptor_t_b200 import capi, parallel
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, lens, H):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    cfg = capi.make_config()
+    assignment = parallel.partition_batch(cfg, lens, world)
+    # "hidden state" of token t of sequence i: row filled with 1000*i + t (fits fp32 exactly)
+    rows = []
+    for i in assignment[rank]:
+        rows.append((1000.0 * i + torch.arange(lens[i], dtype=torch.float32)[:, None] / 4096).expand(lens[i], H))
+    local = torch.cat(rows, 0).contiguous()
+    full = parallel.gather_outputs(local, assignment, lens)
+    exp = torch.cat([(1000.0 * i + torch.arange(n, dtype=torch.float32)[:, None] / 4096).expand(n, H)
+                     for i, n in enumerate(lens)], 0)
+    assert torch.equal(full, exp)
+    dist.destroy_process_group()
+
+
+def test_partition_covers_all_sequences_and_balances():
+    cfg = capi.make_config()
+    rng = np.random.default_rng(0)
+    lens = [int(x) for x in 64 * rng.integers(16, 65, size=64)]
+    for world in (1, 2, 4, 8):
+        a = parallel.partition_batch(cfg, lens, world)
+        assert sorted(i for r in a for i in r) == list(range(len(lens)))
+        costs = parallel.sequence_costs(cfg, lens)
+        loads = [sum(costs[i] for i in r) for r in a]
+        assert max(loads) / (sum(loads) / world) < 1.05
+
+
+def test_gather_restores_input_order_gloo_world2():
+    lens = [1024, 64, 832, 2048, 1472]
+    mp.spawn(_worker, args=(2, _free_port(), lens, 8), nprocs=2, join=True)
