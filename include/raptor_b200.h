@@ -122,10 +122,19 @@ rt_status rt_embeddings(void* out_dev, const int32_t* ids_dev, const int32_t* po
                         int hidden, float eps, int dtype, void* stream);
 
 /* C[M][N] = A[M][K] * W[N][K]^T (+ bias, + GELU), fp32 accumulation on tcgen05 tensor cores.
- * A, W, C 16-bit row-major; K % 64 == 0, N % 64 == 0, 16-byte aligned pointers.
+ * A, W, C 16-bit row-major; K % 64 == 0, N % 64 == 0; A, W, bias 16-byte and C 32-byte aligned.
  * layers/kernels/mat_mul.cpp:9-96 (MatMul; note W here is [out][in], i.e. B transposed). */
 rt_status rt_gemm(void* c_dev, const void* a_dev, const void* w_dev, const void* bias_dev, int M, int N,
                   int K, int epilogue, int dtype, void* stream);
+
+/* Fused QKV projection: (A[M][K] * W[3*heads*64][K]^T + bias), query part scaled by q_scale,
+ * written head-major per sequence straight into q/k/v (the layout of rt_qkv_bias_transpose) -
+ * the [T][3H] intermediate of layers/multi_headed_attention.cpp:143-152 (FuseGemm012AddBIasTranspose)
+ * never touches HBM.  block_seq_dev: int32 pairs {first token of the sequence, sequence length}
+ * for every packed 64-token block. */
+rt_status rt_gemm_qkv(void* q_dev, void* k_dev, void* v_dev, const void* a_dev, const void* w_dev,
+                      const void* bias_dev, const int32_t* block_seq_dev, int M, int heads, int K, float q_scale,
+                      int dtype, void* stream);
 
 /* Attention work list of one layer, built on the host from a CSR block table.
  * A work item covers up to two query blocks of one (sequence, head) so that the tensor-core
@@ -213,7 +222,8 @@ rt_status rt_encoder_get_scratch(rt_encoder* enc, const char* name, void** ptr_d
 rt_status rt_encoder_get_timing(rt_encoder* enc, const char* key, float* ms_out);
 rt_status rt_encoder_enable_timing(rt_encoder* enc, int on);
 rt_status rt_encoder_kernel_launches(rt_encoder* enc, int64_t* launches_out);
-/* options: "fuse_gelu" (1: bias+GELU in the FFN-up GEMM epilogue, 0: separate rt_bias_gelu kernel). */
+/* options: "fuse_gelu" (1: bias+GELU in the FFN-up GEMM epilogue, 0: separate rt_bias_gelu kernel);
+ * "fuse_qkv" (1: rt_gemm_qkv, 0: rt_gemm + rt_qkv_bias_transpose).  Both default to 1. */
 rt_status rt_encoder_set_option(rt_encoder* enc, const char* name, int value);
 /* work-list statistics of one layer of the prepared batch */
 rt_status rt_encoder_plan_stats(rt_encoder* enc, int layer, int64_t* entries_out, int64_t* visits_out,

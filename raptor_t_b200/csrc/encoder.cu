@@ -116,6 +116,7 @@ struct rt_encoder {
   DevBuf emb_word, emb_pos, emb_type, emb_g, emb_b;
   bool emb_set = false;
   bool fuse_gelu = true;
+  bool fuse_qkv = true;
 
   // scratch ("TensorSet")
   std::map<std::string, DevBuf> scratch;
@@ -136,9 +137,10 @@ struct rt_encoder {
     uint8_t* meta_pinned = nullptr;
     size_t meta_cap = 0;
     DevBuf meta_dev;
-    int32_t* prefix_pinned = nullptr;
+    int32_t* prefix_pinned = nullptr;  // [n_seq+1] block prefix sums, then [n_blocks][2] {first token, length}
     int prefix_cap = 0;
     DevBuf prefix_dev;
+    size_t block_seq_off = 0;          // offset (int32 units) of the per-block table
     cudaEvent_t prefix_ready = nullptr;
     cudaEvent_t forward_done = nullptr;
     bool forward_recorded = false;
@@ -339,11 +341,15 @@ rt_status run_attention(rt_encoder* e, int l, const void* input, void* output, c
   void* ctx = e->scratch["attention_out"].p;
   void* dense = e->scratch["dense_out"].p;
   RT_CHECK_CUDA(cudaStreamWaitEvent(st, e->cur->prefix_ready, 0));
-  {
+  if (e->fuse_qkv) {
     Span s(e, st, "gemm");
-    RT_TRY(rt_gemm(qkv, input, w.qkv_w.p, nullptr, T, 3 * H, H, RT_EPI_NONE, dt, st));
-  }
-  {
+    const int32_t* block_seq = static_cast<const int32_t*>(e->cur->prefix_dev.p) + e->cur->block_seq_off;
+    RT_TRY(rt_gemm_qkv(q, k, v, input, w.qkv_w.p, w.qkv_b.p, block_seq, T, c.heads, H, 0.125f, dt, st));
+  } else {
+    {
+      Span s(e, st, "gemm");
+      RT_TRY(rt_gemm(qkv, input, w.qkv_w.p, nullptr, T, 3 * H, H, RT_EPI_NONE, dt, st));
+    }
     Span s(e, st, "add_bias_and_transpose_kernel");
     RT_TRY(rt_qkv_bias_transpose(qkv, w.qkv_b.p, q, k, v, (const int32_t*)e->cur->prefix_dev.p, e->n_seq, e->n_blocks,
                                  c.heads, 0.125f, dt, st));
@@ -513,6 +519,10 @@ extern "C" rt_status rt_encoder_set_option(rt_encoder* e, const char* name, int 
     e->fuse_gelu = value != 0;
     return RT_OK;
   }
+  if (std::strcmp(name, "fuse_qkv") == 0) {
+    e->fuse_qkv = value != 0;
+    return RT_OK;
+  }
   return fail(RT_ERR_INVALID, "set_option: unknown option '%s'", name);
 }
 
@@ -539,16 +549,30 @@ extern "C" rt_status rt_encoder_prepare_batch(rt_encoder* e, const int32_t* lens
   slot.forward_recorded = false;
   e->cur = &slot;
 
-  // varlen offsets
-  if (n_seq + 1 > slot.prefix_cap) {
+  // varlen offsets + per-block {first token of the sequence, sequence length}
+  const int prefix_ints = ((n_seq + 1 + 7) / 8) * 8;  // keeps the block table 32-byte aligned
+  const int need_ints = prefix_ints + 2 * e->n_blocks;
+  if (need_ints > slot.prefix_cap) {
     if (slot.prefix_pinned) cudaFreeHost(slot.prefix_pinned);
     slot.prefix_pinned = nullptr;
-    slot.prefix_cap = std::max(2 * (n_seq + 1), 64);
+    slot.prefix_cap = std::max(2 * need_ints, 1024);
     RT_CHECK_CUDA(cudaMallocHost(&slot.prefix_pinned, slot.prefix_cap * sizeof(int32_t)));
     RT_TRY(slot.prefix_dev.ensure(slot.prefix_cap * sizeof(int32_t)));
   }
   RT_TRY(rt_seq_block_prefix(lens, n_seq, e->cfg.block, slot.prefix_pinned));
-  RT_CHECK_CUDA(cudaMemcpyAsync(slot.prefix_dev.p, slot.prefix_pinned, (n_seq + 1) * sizeof(int32_t),
+  slot.block_seq_off = prefix_ints;
+  {
+    int32_t* bs = slot.prefix_pinned + prefix_ints;
+    int t0 = 0, b = 0;
+    for (int q = 0; q < n_seq; ++q) {
+      for (int i = 0; i < lens[q] / e->cfg.block; ++i, ++b) {
+        bs[2 * b] = t0;
+        bs[2 * b + 1] = lens[q];
+      }
+      t0 += lens[q];
+    }
+  }
+  RT_CHECK_CUDA(cudaMemcpyAsync(slot.prefix_dev.p, slot.prefix_pinned, need_ints * sizeof(int32_t),
                                 cudaMemcpyHostToDevice, e->meta_stream));
   RT_CHECK_CUDA(cudaEventRecord(slot.prefix_ready, e->meta_stream));
 

@@ -64,10 +64,25 @@ __device__ __forceinline__ float2 unpack2(uint32_t w) {
   }
 }
 
+// Extra arguments of the QKV epilogue: the [T][3H] result is never written; each
+// 64-wide head slice of a row goes, with bias added (and the query scaled), straight to
+// the per-sequence head-major q / k / v buffers the attention kernel reads
+// (row (seq_first_token*heads + head*seq_len + token_in_seq) of a [T*heads][64] matrix).
+struct QkvEpilogue {
+  uint16_t* q;
+  uint16_t* k;
+  uint16_t* v;
+  const int2* block_seq;  // per packed 64-token block: {first token of its sequence, sequence length}
+  int heads;
+  float q_scale;
+};
+constexpr int kEpiQkv = 3;
+
 template <int BN, bool BF16, int EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-            uint16_t* __restrict__ C, const uint16_t* __restrict__ bias, int M, int N, int K, int* error_flag) {
+            uint16_t* __restrict__ C, const uint16_t* __restrict__ bias, int M, int N, int K, int* error_flag,
+            QkvEpilogue qkv) {
   using Cfg = GemmCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -198,12 +213,30 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 x0 = gelu_tanh_f(x0);
                 x1 = gelu_tanh_f(x1);
               }
+              if constexpr (EPI == kEpiQkv) {
+                if (n0 + c * 32 < qkv.heads * 64) {  // query part
+                  x0 *= qkv.q_scale;
+                  x1 *= qkv.q_scale;
+                }
+              }
               o[q * 4 + j] = pack2<BF16>(x0, x1);
             }
           }
         }
         if (row < M) {
-          uint16_t* dst = C + static_cast<size_t>(row) * N + n0 + c * 32;
+          uint16_t* dst;
+          if constexpr (EPI == kEpiQkv) {
+            const int hidden = qkv.heads * 64;
+            const int n = n0 + c * 32;
+            const int part = n / hidden;
+            const int hcol = n - part * hidden;
+            const int2 bs = __ldg(qkv.block_seq + (row >> 6));
+            const size_t drow = static_cast<size_t>(bs.x) * qkv.heads + static_cast<size_t>(hcol >> 6) * bs.y +
+                                (row - bs.x);
+            dst = (part == 0 ? qkv.q : part == 1 ? qkv.k : qkv.v) + drow * 64 + (hcol & 63);
+          } else {
+            dst = C + static_cast<size_t>(row) * N + n0 + c * 32;
+          }
           st_global_v8(dst, o);
           st_global_v8(dst + 16, o + 8);
         }
@@ -229,7 +262,8 @@ int gemm_sm_count() {
 }
 
 template <int BN, bool BF16, int EPI>
-rt_status launch(void* c, const void* a, const void* w, const void* bias, int M, int N, int K, cudaStream_t st) {
+rt_status launch(void* c, const void* a, const void* w, const void* bias, int M, int N, int K, cudaStream_t st,
+                 const QkvEpilogue& qkv = QkvEpilogue{}) {
   using Cfg = GemmCfg<BN>;
   CUtensorMap ma, mw;
   RT_TRY(make_tensor_map_2d(&ma, a, M, K, K, kBM, kBK, true));
@@ -244,7 +278,7 @@ rt_status launch(void* c, const void* a, const void* w, const void* bias, int M,
   RT_REQUIRE(err != nullptr, RT_ERR_CUDA, "gemm: cannot allocate the device error word");
   const int tiles = ((M + kBM - 1) / kBM) * (N / BN);
   const int grid = std::min(tiles, gemm_sm_count());
-  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, st>>>(ma, mw, (uint16_t*)c, (const uint16_t*)bias, M, N, K, err);
+  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, st>>>(ma, mw, (uint16_t*)c, (const uint16_t*)bias, M, N, K, err, qkv);
   count_launch();
   RT_CHECK_CUDA(cudaGetLastError());
   return RT_OK;
@@ -273,9 +307,9 @@ extern "C" rt_status rt_gemm(void* c, const void* a, const void* w, const void* 
   RT_REQUIRE(M >= 0 && N > 0 && K > 0 && N % 64 == 0 && K % 64 == 0, RT_ERR_INVALID,
              "gemm: need N %% 64 == 0 and K %% 64 == 0 (got M=%d N=%d K=%d)", M, N, K);
   RT_REQUIRE(epilogue == RT_EPI_NONE || bias != nullptr, RT_ERR_INVALID, "gemm: epilogue needs a bias vector");
-  RT_REQUIRE(((reinterpret_cast<uintptr_t>(c) | reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w) |
-               reinterpret_cast<uintptr_t>(bias)) & 15u) == 0,
-             RT_ERR_INVALID, "gemm: pointers must be 16-byte aligned");
+  RT_REQUIRE(((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(bias)) &
+              15u) == 0 && (reinterpret_cast<uintptr_t>(c) & 31u) == 0,
+             RT_ERR_INVALID, "gemm: A, W and bias must be 16-byte aligned, C 32-byte aligned");
   RT_REQUIRE(dtype == RT_F16 || dtype == RT_BF16, RT_ERR_INVALID, "gemm: unknown dtype %d", dtype);
   if (M == 0) return RT_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -292,4 +326,33 @@ extern "C" rt_status rt_gemm(void* c, const void* a, const void* w, const void* 
                            : launch_epi<128, false>(c, a, w, bias, M, N, K, epilogue, st);
   return bf ? launch_epi<64, true>(c, a, w, bias, M, N, K, epilogue, st)
             : launch_epi<64, false>(c, a, w, bias, M, N, K, epilogue, st);
+}
+
+extern "C" rt_status rt_gemm_qkv(void* q, void* k, void* v, const void* a, const void* w, const void* bias,
+                                 const int32_t* block_seq_dev, int M, int heads, int K, float q_scale, int dtype,
+                                 void* stream) {
+  RT_REQUIRE(q && k && v && a && w && bias && block_seq_dev, RT_ERR_INVALID, "gemm_qkv: null pointer");
+  const int N = 3 * heads * 64;
+  RT_REQUIRE(M >= 0 && M % 64 == 0 && heads > 0 && K > 0 && K % 64 == 0, RT_ERR_INVALID,
+             "gemm_qkv: need M %% 64 == 0 and K %% 64 == 0 (got M=%d heads=%d K=%d)", M, heads, K);
+  RT_REQUIRE(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+               reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(bias)) &
+              31u) == 0,
+             RT_ERR_INVALID, "gemm_qkv: pointers must be 32-byte aligned");
+  RT_REQUIRE(dtype == RT_F16 || dtype == RT_BF16, RT_ERR_INVALID, "gemm_qkv: unknown dtype %d", dtype);
+  if (M == 0) return RT_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  QkvEpilogue e{(uint16_t*)q, (uint16_t*)k, (uint16_t*)v, reinterpret_cast<const int2*>(block_seq_dev), heads,
+                q_scale};
+  const int mt = (M + kBM - 1) / kBM;
+  // tile width must divide 3*heads*64 and keep a 32-column chunk inside one head: 64, 128 and 256 all do
+  const bool wide = N % 256 == 0 && mt * (N / 256) >= 148;
+  const bool mid = N % 128 == 0 && mt * (N / 128) >= 148;
+  const bool bf = dtype == RT_BF16;
+  if (wide) return bf ? launch<256, true, kEpiQkv>(nullptr, a, w, bias, M, N, K, st, e)
+                      : launch<256, false, kEpiQkv>(nullptr, a, w, bias, M, N, K, st, e);
+  if (mid) return bf ? launch<128, true, kEpiQkv>(nullptr, a, w, bias, M, N, K, st, e)
+                     : launch<128, false, kEpiQkv>(nullptr, a, w, bias, M, N, K, st, e);
+  return bf ? launch<64, true, kEpiQkv>(nullptr, a, w, bias, M, N, K, st, e)
+            : launch<64, false, kEpiQkv>(nullptr, a, w, bias, M, N, K, st, e);
 }

@@ -78,6 +78,27 @@ def gemm(a, w, bias=None, epilogue=capi.RT_EPI_NONE, out=None):
     return out
 
 
+def block_seq_table(lens_tokens, device="cuda"):
+    """int32 [N, 2]: for every packed 64-token block {first token of its sequence, sequence length}."""
+    import numpy as np
+    rows, t0 = [], 0
+    for n in lens_tokens:
+        rows += [[t0, int(n)]] * (int(n) // 64)
+        t0 += int(n)
+    return torch.from_numpy(np.asarray(rows, dtype=np.int32).reshape(-1, 2)).to(device)
+
+
+def gemm_qkv(a, w, bias, block_seq, heads, q_scale=0.125, out=None):
+    """Fused QKV projection + bias + query scale + head-major split (no [T,3H] intermediate)."""
+    M, K = a.shape
+    if out is None:
+        out = tuple(torch.empty(M, heads * 64, dtype=a.dtype, device=a.device) for _ in range(3))
+    q, k, v = out
+    check(lib.rt_gemm_qkv(_p(q), _p(k), _p(v), _p(a), _p(w), _p(bias), _p(block_seq), M, heads, K, float(q_scale),
+                          _dt(a), _stream()))
+    return q, k, v
+
+
 class AttentionPlan:
     """Device work list for rt_sparse_attention built from a CSR block table."""
 

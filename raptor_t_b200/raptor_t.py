@@ -55,20 +55,21 @@ def _accumulate(info, key, fn):
 
 
 class TensorSet:
-    """Process-wide scratch buffers resized per batch (layers/tensor_set.h:36-65)."""
+    """Process-wide scratch buffers resized per batch (layers/tensor_set.h:36-65).
+    Buffers are allocated on first use, so the bookkeeping also works without a GPU."""
     _instance = None
-    _lock = threading.Lock()
+    _lock = threading.RLock()
 
     def __init__(self, total_seq_len=4096, to_select_index_len=622, to_select_index_position_len=65,
                  hidden=768, dtype=torch.float16):
         self.hidden, self.dtype = hidden, dtype
-        self.total_seq_len = 0
+        self.total_seq_len = int(total_seq_len)
+        self.capacity = 0
         self.seq_len_info = [0]
         self.to_select_index_len = to_select_index_len
         self.to_select_index_position_len = to_select_index_position_len
         self.tensors = {}
         self.generation = 0
-        self._resize(total_seq_len)
         with TensorSet._lock:
             if TensorSet._instance is None:
                 TensorSet._instance = self
@@ -77,38 +78,40 @@ class TensorSet:
     def get_instance():
         with TensorSet._lock:
             if TensorSet._instance is None:
-                TensorSet._instance = TensorSet.__new__(TensorSet)
-                TensorSet._instance.__init__()
+                TensorSet._instance = TensorSet()
             return TensorSet._instance
 
     def configure(self, hidden, dtype):
         if (hidden, dtype) != (self.hidden, self.dtype):
             self.hidden, self.dtype = hidden, dtype
-            self.tensors = {}
-            self._resize(self.total_seq_len, force=True)
+            self.tensors, self.capacity = {}, 0
 
-    def _resize(self, T, force=False):
+    def _ensure(self):
+        if self.tensors and self.capacity >= self.total_seq_len:
+            return
         if not torch.cuda.is_available():
             raise RuntimeError("raptor_t needs a CUDA device (there is no CPU path)")
-        if T > self.total_seq_len or force or not self.tensors:
-            H = self.hidden
-            mk = lambda cols: torch.empty(T, cols, dtype=self.dtype, device="cuda")  # noqa: E731
-            self.tensors = {"q_out": mk(H), "k_out": mk(H), "v_out": mk(H), "attention_out": mk(H),
-                            "tmp_qkv_out1": mk(3 * H), "dense_out": mk(H)}
-        self.total_seq_len = T
+        T, H = max(self.total_seq_len, 1), self.hidden
+        mk = lambda cols: torch.empty(T, cols, dtype=self.dtype, device="cuda")  # noqa: E731
+        self.tensors = {"q_out": mk(H), "k_out": mk(H), "v_out": mk(H), "attention_out": mk(H),
+                        "tmp_qkv_out1": mk(3 * H), "dense_out": mk(H)}
+        self.capacity = T
 
     def update_tensor_set(self, total_seq_len, to_select_index_len, to_select_index_position_len, seq_len_info=None):
-        self._resize(int(total_seq_len))
+        self.total_seq_len = int(total_seq_len)
         self.to_select_index_len = to_select_index_len
         self.to_select_index_position_len = to_select_index_position_len
         if seq_len_info is not None:
             self.seq_len_info = [int(x) for x in seq_len_info]
         self.generation += 1
 
+    _NAMES = ("q_out", "k_out", "v_out", "attention_out", "tmp_qkv_out1", "dense_out")
+
     def get_tensor(self, name):
-        if name not in self.tensors:
+        if name not in TensorSet._NAMES:
             print("no exists tensor")  # layers/tensor_set.cpp:30-33
             return torch.empty(0)
+        self._ensure()
         return self.tensors[name][: self.total_seq_len]
 
     def lens_tokens(self):
@@ -140,7 +143,7 @@ class MetaData:
             layers = list(MetaData._layers)
             if MetaData._pool is None:
                 MetaData._pool = ThreadPoolExecutor(max_workers=4, thread_name_prefix="raptor_meta")
-        device = torch.cuda.current_device()
+        device = torch.cuda.current_device() if torch.cuda.is_available() else None
         for layer in layers:
             if layer.async_:
                 layer._pending = MetaData._pool.submit(layer._build_plan, lens, device)

@@ -36,6 +36,7 @@ def test_small_encoder_from_ids(dtype, fuse):
     P = oracle.make_weights(cfg, seed=3, nonzero_bias=True)
     enc = _make(cfg, dtype, P)
     enc.set_option("fuse_gelu", fuse)
+    enc.set_option("fuse_qkv", fuse)
     lens = [832, 1024, 512, 64]
     rng = np.random.default_rng(0)
     seqs = [torch.from_numpy(rng.integers(0, cfg.vocab, size=n)).int() for n in lens]

@@ -119,6 +119,29 @@ def test_gemm_epilogues(ops, dtype):
     ops.check_device()
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,lens", [(12, [1024, 64, 832]), (2, [128, 64]), (16, [512, 2048, 4096])])
+def test_gemm_qkv_equals_gemm_plus_transpose(ops, dtype, heads, lens):
+    H, T = heads * 64, sum(lens)
+    g = torch.Generator(device="cuda").manual_seed(T)
+    a = torch.randn(T, H, device="cuda", generator=g).to(dtype)
+    w = (torch.randn(3 * H, H, device="cuda", generator=g) / math.sqrt(H)).to(dtype)
+    bias = torch.randn(3 * H, device="cuda", generator=g).to(dtype)
+    prefix = torch.tensor(oracle.seq_block_prefix(lens), dtype=torch.int32, device="cuda")
+    q, k, v = ops.gemm_qkv(a, w, bias, ops.block_seq_table(lens), heads, 0.125)
+    ops.check_device()
+    full = (a.float() @ w.float().t() + bias.float())
+    t0 = 0
+    for n in lens:
+        for part, got in enumerate((q, k, v)):
+            ref = full[t0:t0 + n, part * H:(part + 1) * H].view(n, heads, 64).permute(1, 0, 2)
+            if part == 0:
+                ref = ref * 0.125
+            blk = got.view(-1)[t0 * H:(t0 + n) * H].view(heads, n, 64).float()
+            assert (blk - ref).abs().max().item() < _tol(dtype) * max(1.0, ref.abs().max().item())
+        t0 += n
+
+
 def _attention_case(ops, dtype, cfg, lens, layer, seed):
     from raptor_t_b200 import capi, metadata
     rc = capi.make_config(hidden=cfg.hidden, heads=cfg.heads, ffn=cfg.ffn, layers=cfg.layers, max_pos=cfg.max_pos,

@@ -1,0 +1,42 @@
+"""The reference's operator API (BertAttention / BertIntermediate / BertOutput / TensorSet /
+MetaData and the Python model layer on top) against the oracle."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from oracle import EncoderConfig
+
+pytestmark = pytest.mark.gpu
+
+
+def test_model_layer_matches_oracle():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from raptor_t_b200 import metadata, raptor_t
+    from raptor_t_b200.modeling_bert import BertModelNoPooler
+    cfg = EncoderConfig(hidden=128, heads=2, ffn=256, layers=2, max_pos=4096, vocab=97)
+    P = oracle.make_weights(cfg, seed=3, nonzero_bias=True)
+    lens = [832, 1024, 512]
+    rng = np.random.default_rng(0)
+    seqs = [torch.from_numpy(rng.integers(0, cfg.vocab, size=n)).int() for n in lens]
+    ref = oracle.encoder_ref(seqs, P, cfg)
+    for async_ in (True, False):
+        model = BertModelNoPooler.from_weights(P, cfg.hidden, cfg.heads, cfg.ffn, cfg.layers, torch.bfloat16, async_)
+        prefix, total_comp, part_off, part_ids = metadata.generate_data_metainfo(lens, 64, 160, cfg.heads)
+        T = sum(lens)
+        md = raptor_t.MetaData()
+        md.update_meta_data(T, prefix[-1] + 1, total_comp, prefix)
+        ids = torch.cat(seqs).cuda()
+        pos = torch.cat([torch.arange(n, dtype=torch.int32) for n in lens]).cuda()
+        info = {"pre_process": 0.0, "attention": 0.0, "add_bias_act_kernel": 0.0,
+                "add_bias_and_layernorm_kernel": 0.0, "add_bias_and_transpose_kernel": 0.0}
+        out, info = model(ids, T, 160, prefix, torch.tensor(prefix, dtype=torch.int32, device="cuda"),
+                          torch.from_numpy(part_off).cuda(), torch.from_numpy(part_ids).cuda(),
+                          position_ids=pos, test_info=info)
+        err = (out.float().cpu() - ref).abs()
+        assert err.max().item() < 6e-2 and err.mean().item() < 6e-3
+        assert info["attention"] > 0 and info["add_bias_and_layernorm_kernel"] > 0
+        md.terminate_thread()
+    ts = raptor_t.TensorSet.get_instance()
+    assert ts.get_tensor("q_out").shape[0] == T and ts.get_tensor("nope").numel() == 0
