@@ -31,8 +31,9 @@ class RtError(RuntimeError):
 
 
 def _load():
-    # build() is a no-op when the library is newer than every source file
-    path = _build.build(force=bool(os.environ.get("RAPTOR_B200_REBUILD")))
+    # RAPTOR_B200_LIB selects an explicitly built library (e.g. an instrumented build);
+    # otherwise build() is a no-op when the library is newer than every source file
+    path = os.environ.get("RAPTOR_B200_LIB") or _build.build(force=bool(os.environ.get("RAPTOR_B200_REBUILD")))
     return C.CDLL(path)
 
 

@@ -47,7 +47,9 @@ namespace {
 using namespace ptx;
 
 constexpr int kThreads = 192;
-constexpr int kStages = 4;               // K/V ring depth
+constexpr int kStagesK = 4;              // K ring depth (a slot is free again once the S MMA has read it)
+constexpr int kStagesV = 5;              // V ring depth (a slot is held until the PV MMA, two softmax periods later)
+constexpr int kMaskRing = 16;            // entry masks travel from the producer to the softmax warps through smem
 constexpr int kTileBytes = 64 * 64 * 2;  // one 64 x 64 16-bit block
 constexpr int kQBytes = 2 * kTileBytes;
 constexpr int kTmemCols = 256;
@@ -58,15 +60,16 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 struct Smem {
   uint8_t q[2][kQBytes];
-  uint8_t k[kStages][kTileBytes];
-  uint8_t v[kStages][kTileBytes];
+  uint8_t k[kStagesK][kTileBytes];
+  uint8_t v[kStagesV][kTileBytes];
   uint64_t q_full[2], q_empty[2];
-  uint64_t k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
+  uint64_t k_full[kStagesK], k_empty[kStagesK], v_full[kStagesV], v_empty[kStagesV];
   uint64_t s_full[2], s_free[2], p_full[2], pv_done[2], o_free;
+  int32_t mask_ring[kMaskRing];
   uint32_t tmem_slot;
   int abort_flag;
 };
-constexpr int kSmemBytes = sizeof(Smem) + 1024;
+constexpr int kSmemBytes = sizeof(Smem);
 
 __device__ __forceinline__ float ex2(float x) {
   float y;
@@ -85,16 +88,34 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
   }
 }
 
+// Optional phase timing (compiled in only with -DRT_ATTN_PROFILE, for tuning): lane 0 of
+// every warp adds the SM clocks it spends in each phase to a global table.
+#ifdef RT_ATTN_PROFILE
+__device__ unsigned long long g_attn_prof[16];
+__device__ unsigned long long g_attn_cta_log[1024 * 3];  // per CTA: sm id, start ns, end ns
+#define PROF_DECL long long _pt = clock64(); unsigned long long _pb[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#define PROF_MARK(i) { long long _n = clock64(); _pb[i] += (unsigned long long)(_n - _pt); _pt = _n; }
+#define PROF_FLUSH(base) { if ((threadIdx.x & 31) == 0) for (int _i = 0; _i < 8; ++_i) if (_pb[_i]) atomicAdd(&g_attn_prof[(base) + _i], _pb[_i]); }
+#else
+#define PROF_DECL
+#define PROF_MARK(i)
+#define PROF_FLUSH(base)
+#endif
+
 template <bool BF16>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __maxnreg__(160)
 sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, uint16_t* __restrict__ ctx,
                         const AttnItem* __restrict__ items, const int32_t* __restrict__ entries,
                         const int32_t* __restrict__ cta_ptr, int hidden, float scale_log2, int* error_flag) {
-  extern __shared__ uint8_t smem_raw[];
-  Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  if ((smem_u32(smem_raw) & 1023u) != 0) {  // the swizzled tiles need 1024-byte alignment
+    if (threadIdx.x == 0) atomicCAS(error_flag, 0, 299);
+    return;
+  }
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
@@ -106,9 +127,11 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       mbar_init(&sm.pv_done[i], 1);
     }
     mbar_init(&sm.o_free, 128);
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < kStagesK; ++s) {
       mbar_init(&sm.k_full[s], 1);
       mbar_init(&sm.k_empty[s], 1);
+    }
+    for (int s = 0; s < kStagesV; ++s) {
       mbar_init(&sm.v_full[s], 1);
       mbar_init(&sm.v_empty[s], 1);
     }
@@ -127,36 +150,96 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 
   const int item_begin = cta_ptr[blockIdx.x];
   const int item_end = cta_ptr[blockIdx.x + 1];
+#ifdef RT_ATTN_PROFILE
+  if (threadIdx.x == 0 && blockIdx.x < 1024) {
+    unsigned smid;
+    unsigned long long t;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    g_attn_cta_log[blockIdx.x * 3] = smid;
+    g_attn_cta_log[blockIdx.x * 3 + 1] = t;
+  }
+#endif
 
   if (warp == 4) {
     // ------------------------------------------------------------------ TMA producer
+    // One thread feeds two rings from the same flattened (item, entry) stream with two
+    // cursors: the K cursor (which also loads each item's Q tile and publishes the entry
+    // masks) may run ahead of the V cursor, because K slots are recycled earlier.
     if (lane == 0) {
       prefetch_tensormap(&map_q);
       prefetch_tensormap(&map_k);
       prefetch_tensormap(&map_v);
-      uint32_t g = 0, itn = 0;
-      bool ok = true;
-      for (int it = item_begin; it < item_end && ok; ++it, ++itn) {
-        const AttnItem item = items[it];
-        const int qb = itn & 1;
-        if (!mbar_wait(&sm.q_empty[qb], ((itn >> 1) & 1) ^ 1, ab, 201)) break;
-        mbar_arrive_expect_tx(&sm.q_full[qb], kQBytes);
-        tma_load_2d(sm.q[qb], &map_q, 0, item.q_row0, &sm.q_full[qb]);
-        tma_load_2d(sm.q[qb] + kTileBytes, &map_q, 0, item.q_row1, &sm.q_full[qb]);
-        for (int j = 0; j < item.n_entries; ++j, ++g) {
-          const int s = g % kStages;
-          const uint32_t ph = (g / kStages) & 1;
-          const int row = item.kv_row0 + (entries[item.entry_off + j] >> 2) * 64;
-          if (!mbar_wait(&sm.k_empty[s], ph ^ 1, ab, 202)) { ok = false; break; }
-          mbar_arrive_expect_tx(&sm.k_full[s], kTileBytes);
-          tma_load_2d(sm.k[s], &map_k, 0, row, &sm.k_full[s]);
-          if (!mbar_wait(&sm.v_empty[s], ph ^ 1, ab, 203)) { ok = false; break; }
-          mbar_arrive_expect_tx(&sm.v_full[s], kTileBytes);
-          tma_load_2d(sm.v[s], &map_v, 0, row, &sm.v_full[s]);
+      int k_item = item_begin, k_j = 0, v_item = item_begin, v_j = 0;
+      uint32_t k_g = 0, v_g = 0, k_itn = 0;
+      AttnItem ki{}, vi{};
+      auto load_item = [&](int& item, AttnItem& dst) {
+        while (item < item_end) {
+          dst = items[item];
+          if (dst.n_entries > 0) break;
+          ++item;
+        }
+      };
+      load_item(k_item, ki);
+      load_item(v_item, vi);
+      bool q_loaded = false;
+      long long idle_since = clock64();
+      volatile int* abort_flag = &sm.abort_flag;
+      while ((k_item < item_end || v_item < item_end) && !*abort_flag) {
+        bool progress = false;
+        if (k_item < item_end) {
+          const int qb = k_itn & 1;
+          if (!q_loaded && mbar_test_wait(&sm.q_empty[qb], ((k_itn >> 1) & 1) ^ 1)) {
+            mbar_arrive_expect_tx(&sm.q_full[qb], kQBytes);
+            tma_load_2d(sm.q[qb], &map_q, 0, ki.q_row0, &sm.q_full[qb]);
+            tma_load_2d(sm.q[qb] + kTileBytes, &map_q, 0, ki.q_row1, &sm.q_full[qb]);
+            q_loaded = true;
+            progress = true;
+          }
+          const int s = k_g % kStagesK;
+          if (q_loaded && mbar_test_wait(&sm.k_empty[s], ((k_g / kStagesK) & 1) ^ 1)) {
+            const int e = entries[ki.entry_off + k_j];
+            sm.mask_ring[k_g % kMaskRing] = e & 3;
+            mbar_arrive_expect_tx(&sm.k_full[s], kTileBytes);
+            tma_load_2d(sm.k[s], &map_k, 0, ki.kv_row0 + (e >> 2) * 64, &sm.k_full[s]);
+            ++k_g;
+            if (++k_j == ki.n_entries) {
+              ++k_item;
+              ++k_itn;
+              k_j = 0;
+              q_loaded = false;
+              load_item(k_item, ki);
+            }
+            progress = true;
+          }
+        }
+        if (v_item < item_end && v_g < k_g) {
+          const int s = v_g % kStagesV;
+          if (mbar_test_wait(&sm.v_empty[s], ((v_g / kStagesV) & 1) ^ 1)) {
+            const int e = entries[vi.entry_off + v_j];
+            mbar_arrive_expect_tx(&sm.v_full[s], kTileBytes);
+            tma_load_2d(sm.v[s], &map_v, 0, vi.kv_row0 + (e >> 2) * 64, &sm.v_full[s]);
+            ++v_g;
+            if (++v_j == vi.n_entries) {
+              ++v_item;
+              v_j = 0;
+              load_item(v_item, vi);
+            }
+            progress = true;
+          }
+        }
+        if (progress) {
+          idle_since = clock64();
+        } else {
+          __nanosleep(100);  // both rings full: stay off the issue slots of the softmax warp on this scheduler
+          if (clock64() - idle_since > kWaitCycles) {
+            *abort_flag = 1;
+            atomicCAS(error_flag, 0, 201);
+          }
         }
       }
-      // A wait gives up only after the pipeline has been idle for the whole time-out,
-      // so none of this thread's copies can still be in flight when it gets here.
+      // Leaving on an abort happens only after the pipeline has been idle for the whole
+      // time-out, so none of this thread's copies can still be in flight.
     }
   } else if (warp == 5) {
     // ------------------------------------------------------------------ MMA issuer
@@ -182,8 +265,8 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         }
         const int b = s_g & 1;
         const uint32_t u = s_g >> 1;
-        const int st = s_g % kStages;
-        const uint32_t ph = (s_g / kStages) & 1;
+        const int st = s_g % kStagesK;
+        const uint32_t ph = (s_g / kStagesK) & 1;
         if (!mbar_wait(&sm.k_full[st], ph, ab, 212)) return false;
         if (!mbar_wait(&sm.s_free[b], (u & 1) ^ 1, ab, 213)) return false;
         tc_fence_after_sync();
@@ -208,8 +291,8 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       auto issue_pv = [&]() -> bool {
         const int b = pv_g & 1;
         const uint32_t u = pv_g >> 1;
-        const int st = pv_g % kStages;
-        const uint32_t ph = (pv_g / kStages) & 1;
+        const int st = pv_g % kStagesV;
+        const uint32_t ph = (pv_g / kStagesV) & 1;
         if (!mbar_wait(&sm.v_full[st], ph, ab, 214)) return false;
         if (pv_j == 0) {
           // the output tile is overwritten: the softmax warps must have read the previous item's result
@@ -247,8 +330,11 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
     uint32_t g = 0, itn = 0;
     bool ok = true;
+    PROF_DECL
+    AttnItem next_item = item_begin < item_end ? items[item_begin] : AttnItem{};
     for (int it = item_begin; it < item_end && ok; ++it) {
-      const AttnItem item = items[it];
+      const AttnItem item = next_item;
+      if (it + 1 < item_end) next_item = items[it + 1];  // in flight while this item is processed
       const int n = item.n_entries;
       if (n == 0) continue;
       float m_ref = -INFINITY;  // max the stored probabilities / output are relative to (log2 units)
@@ -257,9 +343,12 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         const uint32_t gj = g + j;
         const int b = gj & 1;
         const uint32_t u = gj >> 1;
-        const bool active = ((entries[item.entry_off + j] >> half) & 1) != 0;
+        PROF_MARK(0)
         if (!mbar_wait(&sm.s_full[b], u & 1, ab, 221)) { ok = false; break; }
+        PROF_MARK(1)
         tc_fence_after_sync();
+        // the producer published this entry's mask before it loaded the K block of the S tile just waited for
+        const bool active = ((sm.mask_ring[gj % kMaskRing] >> half) & 1) != 0;
         uint32_t s[64];
         if (active) {
           tmem_ld32(lane_base + kColS + b * 64, s);
@@ -268,6 +357,7 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         }
         tc_fence_before_sync();
         mbar_arrive(&sm.s_free[b]);
+        PROF_MARK(2)
         float alpha = 1.f;
         bool fix = false;
         if (active) {
@@ -291,7 +381,9 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         }
         // the probability buffer was last read by the PV MMA two entries back
         if (gj >= 2) {
+          PROF_MARK(3)
           if (!mbar_wait(&sm.pv_done[b], ((gj - 2) >> 1) & 1, ab, 222)) { ok = false; break; }
+          PROF_MARK(4)
         }
         if (__any_sync(0xffffffffu, fix)) {
           // rescale this warp's rows of the output tile; every PV MMA issued so far must be done
@@ -333,44 +425,62 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           tmem_st16(lane_base + kColP + b * 32, p);
           tmem_st16(lane_base + kColP + b * 32 + 16, p);
         }
+        PROF_MARK(5)
         tc_wait_st();
         tc_fence_before_sync();
         mbar_arrive(&sm.p_full[b]);
+        PROF_MARK(6)
       }
       if (!ok) break;
       g += n;
       // final: the last PV MMA of the item completes the output tile
       {
         const uint32_t gl = g - 1;
+        PROF_MARK(0)
         if (!mbar_wait(&sm.pv_done[gl & 1], (gl >> 1) & 1, ab, 224)) { ok = false; break; }
+        PROF_MARK(7)
         tc_fence_after_sync();
       }
       const int tok0 = half == 0 ? item.out_tok0 : item.out_tok1;
-      uint32_t o[64];
-      if (tok0 >= 0) {
-        tmem_ld32(lane_base + kColO, o);
-        tmem_ld32(lane_base + kColO + 32, o + 32);
-        tc_wait_ld();
-      }
-      tc_fence_before_sync();
-      mbar_arrive(&sm.o_free);
-      ++itn;
-      if (tok0 >= 0) {
-        const float inv = 1.0f / l;
-        uint16_t* dst = ctx + static_cast<size_t>(tok0 + (row & 63)) * hidden + item.head * 64;
+      const float inv = 1.0f / l;
+      uint16_t* dst = ctx + static_cast<size_t>((tok0 >= 0 ? tok0 : 0) + (row & 63)) * hidden + item.head * 64;
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          uint32_t w[8];
+      for (int hc = 0; hc < 2; ++hc) {
+        uint32_t o[32];
+        if (tok0 >= 0) {
+          tmem_ld32(lane_base + kColO + hc * 32, o);
+          tc_wait_ld();
+        }
+        if (hc == 1) {
+          // both halves are in registers: the MMA warp may overwrite the output tile
+          tc_fence_before_sync();
+          mbar_arrive(&sm.o_free);
+        }
+        if (tok0 >= 0) {
 #pragma unroll
-          for (int e = 0; e < 8; ++e)
-            w[e] = pack2<BF16>(__uint_as_float(o[16 * q + 2 * e]) * inv, __uint_as_float(o[16 * q + 2 * e + 1]) * inv);
-          st_global_v8(dst + 16 * q, w);
+          for (int q = 0; q < 2; ++q) {
+            uint32_t w[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+              w[e] = pack2<BF16>(__uint_as_float(o[16 * q + 2 * e]) * inv, __uint_as_float(o[16 * q + 2 * e + 1]) * inv);
+            st_global_v8(dst + hc * 32 + 16 * q, w);
+          }
         }
       }
+      ++itn;
     }
     (void)itn;
+    PROF_MARK(0)
+    PROF_FLUSH(0)
   }
 
+#ifdef RT_ATTN_PROFILE
+  if (threadIdx.x == 0 && blockIdx.x < 1024) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    g_attn_cta_log[blockIdx.x * 3 + 2] = t;
+  }
+#endif
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 5) {
@@ -400,6 +510,9 @@ rt_status launch_sparse_attention(void* ctx, const void* q, const void* k, const
     if (!set) {
       RT_CHECK_CUDA(cudaFuncSetAttribute(sparse_attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          kSmemBytes));
+      // two CTAs per SM need the largest shared-memory carve-out
+      RT_CHECK_CUDA(cudaFuncSetAttribute(sparse_attention_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                         cudaSharedmemCarveoutMaxShared));
       set = true;
     }
     sparse_attention_kernel<true><<<n_ctas, kThreads, kSmemBytes, st>>>(mq, mk, mv, (uint16_t*)ctx, items_dev,
@@ -410,6 +523,8 @@ rt_status launch_sparse_attention(void* ctx, const void* q, const void* k, const
     if (!set) {
       RT_CHECK_CUDA(cudaFuncSetAttribute(sparse_attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          kSmemBytes));
+      RT_CHECK_CUDA(cudaFuncSetAttribute(sparse_attention_kernel<false>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                         cudaSharedmemCarveoutMaxShared));
       set = true;
     }
     sparse_attention_kernel<false><<<n_ctas, kThreads, kSmemBytes, st>>>(mq, mk, mv, (uint16_t*)ctx, items_dev,
@@ -420,6 +535,7 @@ rt_status launch_sparse_attention(void* ctx, const void* q, const void* k, const
   RT_CHECK_CUDA(cudaGetLastError());
   return RT_OK;
 }
+
 
 }  // namespace rt
 
@@ -508,3 +624,21 @@ extern "C" rt_status rt_sparse_attention(void* ctx, const void* q, const void* k
                                  plan->host.total_tokens, plan->host.heads, scale, dtype,
                                  static_cast<cudaStream_t>(stream));
 }
+
+#ifdef RT_ATTN_PROFILE
+// Tuning builds only: read (and optionally clear) the phase-clock table.
+extern "C" rt_status rt_attn_cta_log_read(unsigned long long* out, int n_ctas) {
+  RT_CHECK_CUDA(cudaDeviceSynchronize());
+  RT_CHECK_CUDA(cudaMemcpyFromSymbol(out, rt::g_attn_cta_log, sizeof(unsigned long long) * 3 * n_ctas));
+  return RT_OK;
+}
+extern "C" rt_status rt_attn_profile_read(unsigned long long* out16, int reset) {
+  RT_CHECK_CUDA(cudaDeviceSynchronize());
+  RT_CHECK_CUDA(cudaMemcpyFromSymbol(out16, rt::g_attn_prof, sizeof(unsigned long long) * 16));
+  if (reset) {
+    unsigned long long z[16] = {0};
+    RT_CHECK_CUDA(cudaMemcpyToSymbol(rt::g_attn_prof, z, sizeof(z)));
+  }
+  return RT_OK;
+}
+#endif
