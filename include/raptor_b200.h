@@ -166,6 +166,24 @@ rt_status rt_attn_plan_build_host(const rt_config* cfg, uint32_t layer_seed, con
 rt_status rt_sparse_attention(void* ctx_dev, const void* q_dev, const void* k_dev, const void* v_dev,
                               const rt_attn_plan* plan, float scale, int dtype, void* stream);
 
+/* Block-sparse attention WITHOUT any device allocation.  No counterpart in the reference.
+ * For callers that may not call cudaMalloc (memory owned by an external arena or caching
+ * allocator, a fixed start-up budget, a thread that must not hit an implicit device
+ * synchronisation): the work list and the status word live in a file-scope device array of
+ * about 0.78 MB that each GPU holds from library load until exit.  Same math and layouts as
+ * rt_sparse_attention; the block table is given as HOST CSR arrays (rt_build_block_csr).
+ * Limits: at most 8192 work items and 131072 list entries per call (about 26 sequences of 4096
+ * tokens with 12 heads), else RT_ERR_UNSUPPORTED and nothing runs.  The array is shared by all
+ * calls on a device and keeps the last call's contents; calls whose GPU work overlaps race on
+ * it, so issue them on one stream.  The first call on a device resolves the array's address
+ * and sets kernel attributes: make it before any stream capture.  Each call first reads back
+ * (blocking, 4 bytes) and clears the status of the previous call, so a kernel that gave up on a
+ * bounded wait is reported by the following call. */
+rt_status rt_sparse_attention_static(void* ctx_dev, const void* q_dev, const void* k_dev, const void* v_dev,
+                                     const rt_config* cfg, const int32_t* lens_tokens_host, int n_seq,
+                                     const int32_t* kv_ptr_host, const int32_t* kv_idx_host, float scale,
+                                     int dtype, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * Encoder object: weights, scratch (the TensorSet), metadata pipeline, streams and events.
  * ---------------------------------------------------------------------------------------- */

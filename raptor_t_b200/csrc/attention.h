@@ -1,3 +1,5 @@
+// error_word_dev: device word the kernel reports a given-up wait in; nullptr selects the
+// library's per-device word (allocated on first use).
 // Internal launcher of the block-sparse attention kernel (device work list given
 // as raw pointers) shared by the C ABI and the encoder object.
 #pragma once
@@ -11,6 +13,7 @@ rt_status check_config(const rt_config* cfg);
 
 rt_status launch_sparse_attention(void* ctx, const void* q, const void* k, const void* v, const AttnItem* items_dev,
                                   const int32_t* entries_dev, const int32_t* cta_ptr_dev, int n_ctas,
-                                  int total_tokens, int heads, float scale, int dtype, cudaStream_t st);
+                                  int total_tokens, int heads, float scale, int dtype, cudaStream_t st,
+                                  int* error_word_dev = nullptr);
 
 }  // namespace rt

@@ -493,7 +493,7 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 
 rt_status launch_sparse_attention(void* ctx, const void* q, const void* k, const void* v, const AttnItem* items_dev,
                                   const int32_t* entries_dev, const int32_t* cta_ptr_dev, int n_ctas,
-                                  int total_tokens, int heads, float scale, int dtype, cudaStream_t st) {
+                                  int total_tokens, int heads, float scale, int dtype, cudaStream_t st, int* error_word_dev) {
   RT_REQUIRE(dtype == RT_F16 || dtype == RT_BF16, RT_ERR_INVALID, "sparse_attention: unknown dtype %d", dtype);
   RT_REQUIRE(n_ctas > 0 && total_tokens > 0 && heads > 0, RT_ERR_INVALID, "sparse_attention: empty plan");
   const uint64_t rows = static_cast<uint64_t>(total_tokens) * heads;
@@ -501,7 +501,7 @@ rt_status launch_sparse_attention(void* ctx, const void* q, const void* k, const
   RT_TRY(make_tensor_map_2d(&mq, q, rows, 64, 64, 64, 64, true));
   RT_TRY(make_tensor_map_2d(&mk, k, rows, 64, 64, 64, 64, true));
   RT_TRY(make_tensor_map_2d(&mv, v, rows, 64, 64, 64, 64, true));
-  int* err = device_error_word();
+  int* err = error_word_dev ? error_word_dev : device_error_word();
   RT_REQUIRE(err != nullptr, RT_ERR_CUDA, "sparse_attention: cannot allocate the device error word");
   const float scale_log2 = scale * 1.4426950408889634f;
   const int hidden = heads * 64;

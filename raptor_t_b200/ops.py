@@ -139,6 +139,24 @@ def sparse_attention(q, k, v, plan, scale=1.0, out=None):
     return out
 
 
+def sparse_attention_static(q, k, v, cfg, lens_tokens, kv_ptr, kv_idx, scale=1.0, out=None):
+    """Same result as sparse_attention, for callers that must not allocate device memory: the
+    work list goes into the library's fixed device array instead of an AttentionPlan (see
+    rt_sparse_attention_static in include/raptor_b200.h for the size limit and sharing rules).
+    `out` must be given by such callers; it is only created here for convenience."""
+    import numpy as np
+    if out is None:
+        out = torch.empty_like(q)
+    lens = np.ascontiguousarray(lens_tokens, dtype=np.int32)
+    kv_ptr = np.ascontiguousarray(kv_ptr, dtype=np.int32)
+    kv_idx = np.ascontiguousarray(kv_idx, dtype=np.int32)
+    i32p = C.POINTER(C.c_int32)
+    check(lib.rt_sparse_attention_static(_p(out), _p(q), _p(k), _p(v), C.byref(cfg), lens.ctypes.data_as(i32p),
+                                         len(lens), kv_ptr.ctypes.data_as(i32p), kv_idx.ctypes.data_as(i32p),
+                                         float(scale), _dt(q), _stream()))
+    return out
+
+
 def check_device():
     """Synchronise and raise if any kernel gave up on a bounded device-side wait."""
     check(lib.rt_check_device())
