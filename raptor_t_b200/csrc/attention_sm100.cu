@@ -77,6 +77,32 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// Packed fp32x2 arithmetic and three-input max (sm_100): half the issue slots of the
+// scalar forms in the softmax inner loops.
+__device__ __forceinline__ unsigned long long f2_pack(float a, float b) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(unsigned long long v, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long f2_fma(unsigned long long a, unsigned long long b, unsigned long long c) {
+  unsigned long long r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ unsigned long long f2_add(unsigned long long a, unsigned long long b) {
+  unsigned long long r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
 template <bool BF16>
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
   if constexpr (BF16) {
@@ -364,12 +390,14 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           float mx0 = __uint_as_float(s[0]), mx1 = __uint_as_float(s[1]);
           float mx2 = __uint_as_float(s[2]), mx3 = __uint_as_float(s[3]);
 #pragma unroll
-          for (int i = 4; i < 64; i += 4) {
-            mx0 = fmaxf(mx0, __uint_as_float(s[i]));
-            mx1 = fmaxf(mx1, __uint_as_float(s[i + 1]));
-            mx2 = fmaxf(mx2, __uint_as_float(s[i + 2]));
-            mx3 = fmaxf(mx3, __uint_as_float(s[i + 3]));
+          for (int i = 4; i < 60; i += 8) {
+            mx0 = max3(mx0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+            mx1 = max3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+            mx2 = max3(mx2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
+            mx3 = max3(mx3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
           }
+          mx0 = max3(mx0, __uint_as_float(s[60]), __uint_as_float(s[61]));
+          mx1 = max3(mx1, __uint_as_float(s[62]), __uint_as_float(s[63]));
           const float m_new = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;
           if (m_ref == -INFINITY) {
             m_ref = m_new;  // nothing accumulated for this row yet (its output columns are still zero)
@@ -403,21 +431,28 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           l *= alpha;
         }
         if (active) {
-          float sum0 = 0.f, sum1 = 0.f;
+          const unsigned long long c2 = f2_pack(scale_log2, scale_log2);
+          const unsigned long long nm2 = f2_pack(-m_ref, -m_ref);
+          unsigned long long acc0 = 0ull, acc1 = 0ull;  // two packed partial sums (+0.0f, +0.0f)
 #pragma unroll
           for (int hc = 0; hc < 2; ++hc) {
             uint32_t p[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-              const float p0 = ex2(fmaf(__uint_as_float(s[32 * hc + 2 * i]), scale_log2, -m_ref));
-              const float p1 = ex2(fmaf(__uint_as_float(s[32 * hc + 2 * i + 1]), scale_log2, -m_ref));
-              sum0 += p0;
-              sum1 += p1;
+              const unsigned long long t =
+                  f2_fma(f2_pack(__uint_as_float(s[32 * hc + 2 * i]), __uint_as_float(s[32 * hc + 2 * i + 1])), c2, nm2);
+              float t0, t1;
+              f2_unpack(t, t0, t1);
+              const float p0 = ex2(t0), p1 = ex2(t1);
+              if (i & 1) acc1 = f2_add(acc1, f2_pack(p0, p1));
+              else acc0 = f2_add(acc0, f2_pack(p0, p1));
               p[i] = pack2<BF16>(p0, p1);
             }
             tmem_st16(lane_base + kColP + b * 32 + hc * 16, p);
           }
-          l += sum0 + sum1;
+          float s0, s1;
+          f2_unpack(f2_add(acc0, acc1), s0, s1);
+          l += s0 + s1;
         } else {
           uint32_t p[16];
 #pragma unroll

@@ -9,7 +9,7 @@ python/benchmark/attention_test.py and mem_bound_op.py, re-stated for this libra
     python -m raptor_t_b200.microbench --kernel all
 
 Each line of output is one JSON object: algorithmic FLOPs or bytes, the median CUDA-event
-time over --iters launches (L2 flushed before each), and the achieved rate as a fraction
+time over --iters launches (L2 flushed before each: 256 MiB written, then read back), and the achieved rate as a fraction
 of the measured peaks in MEASURED_PEAKS.json (fallback 6650 GB/s / 1590 TFLOP/s).
 Attention FLOPs count listed (query block, key block) pairs only: 4*64*64*64 per pair.
 """
@@ -48,7 +48,10 @@ def _time(fn, iters, warmup=3, flush=True):
     ts = []
     for _ in range(iters):
         if flush:
+            # write 256 MiB (evicts everything), then read it back: the read sweep forces the
+            # dirty lines out, so the timed kernel starts on a cold L2 without write-back debt
             _FLUSH.fill_(0)
+            _FLUSH.view(torch.int64).sum()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         fn()
