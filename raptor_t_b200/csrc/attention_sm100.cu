@@ -6,12 +6,15 @@
 // random blocks come from the same table; each entry carries a 2-bit mask that
 // says which of the two query blocks uses it).
 //
-//   warp 4   TMA producer: Q tile per item, then one K box and one V box
-//            (64 x 64, 128-byte swizzle) per list entry into a shared-memory ring;
-//   warp 5   MMA issuer:   S = Q K^T  (M=128, N=64, K=64; both operands K-major in
-//            shared memory) into one of two TMEM score buffers, and
-//            PV = P V (P read from TMEM, V MN-major in shared memory) into one of
-//            two TMEM result buffers.  S of entry j+1 is issued before PV of entry j;
+//   warp 4   one thread runs a polling loop over three jobs: TMA loads of the Q tile
+//            per item and of one K box and one V box (64 x 64, 128-byte swizzle) per
+//            list entry into two shared-memory rings, and the issue of S = Q K^T
+//            (M=128, N=64, K=64; both operands K-major in shared memory) into one of
+//            two TMEM score buffers as soon as its K block has landed;
+//   warp 5   one thread issues PV = P V (P read from TMEM, V MN-major in shared
+//            memory), accumulating the output tile in TMEM.  Splitting the two MMA
+//            issue chains over two threads matters: each chain (barrier polls, four
+//            K=16 MMAs, commits) costs about a thousand clocks per entry;
 //   warps 0-3  softmax: thread r owns tile row r.  It pulls its score row out of
 //            TMEM, keeps the running max / sum in fp32 (base-2 exponentials) and
 //            writes the 16-bit probabilities back to TMEM for the PV MMA.  The
@@ -116,6 +119,22 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 
 // Optional phase timing (compiled in only with -DRT_ATTN_PROFILE, for tuning): lane 0 of
 // every warp adds the SM clocks it spends in each phase to a global table.
+#ifdef RT_ATTN_TRACE
+// Tuning builds only: lane 0 of every warp of CTA 0 logs (clock, event, index) into its own
+// slice with plain stores.
+__device__ unsigned long long g_trace[8 * 1024 * 2];
+#define TRACE_DECL unsigned _tr_i = 0;
+#define TRACE(ev, idx)                                                                      \
+  if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && _tr_i < 1024) {                         \
+    unsigned long long* _p = g_trace + ((threadIdx.x >> 5) * 1024 + _tr_i) * 2;             \
+    _p[0] = clock64();                                                                      \
+    _p[1] = (static_cast<unsigned long long>(ev) << 32) | static_cast<unsigned>(idx);       \
+    ++_tr_i;                                                                                \
+  }
+#else
+#define TRACE_DECL
+#define TRACE(ev, idx)
+#endif
 #ifdef RT_ATTN_PROFILE
 __device__ unsigned long long g_attn_prof[16];
 __device__ unsigned long long g_attn_cta_log[1024 * 3];  // per CTA: sm id, start ns, end ns
@@ -176,6 +195,7 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 
   const int item_begin = cta_ptr[blockIdx.x];
   const int item_end = cta_ptr[blockIdx.x + 1];
+  TRACE_DECL
 #ifdef RT_ATTN_PROFILE
   if (threadIdx.x == 0 && blockIdx.x < 1024) {
     unsigned smid;
@@ -196,9 +216,16 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       prefetch_tensormap(&map_q);
       prefetch_tensormap(&map_k);
       prefetch_tensormap(&map_v);
+      constexpr uint32_t idesc_s = make_idesc_f16(128, 64, BF16 ? 1 : 0, false);
       int k_item = item_begin, k_j = 0, v_item = item_begin, v_j = 0;
       uint32_t k_g = 0, v_g = 0, k_itn = 0;
       AttnItem ki{}, vi{};
+      int s_item = item_begin, s_j = 0, s_n = 0;  // S = Q K^T issue cursor (behind the K cursor)
+      uint32_t s_g = 0, s_itn = 0;
+      auto next_s_item = [&]() {
+        while (s_item < item_end && (s_n = items[s_item].n_entries) == 0) ++s_item;
+      };
+      next_s_item();
       auto load_item = [&](int& item, AttnItem& dst) {
         while (item < item_end) {
           dst = items[item];
@@ -211,8 +238,35 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       bool q_loaded = false;
       long long idle_since = clock64();
       volatile int* abort_flag = &sm.abort_flag;
-      while ((k_item < item_end || v_item < item_end) && !*abort_flag) {
+      while ((k_item < item_end || v_item < item_end || s_item < item_end) && !*abort_flag) {
         bool progress = false;
+        if (s_item < item_end && s_g < k_g) {
+          const int qb = s_itn & 1;
+          const int b = s_g & 1;
+          const int st = s_g % kStagesK;
+          if ((s_j > 0 || mbar_test_wait(&sm.q_full[qb], (s_itn >> 1) & 1)) &&
+              mbar_test_wait(&sm.k_full[st], (s_g / kStagesK) & 1) &&
+              mbar_test_wait(&sm.s_free[b], ((s_g >> 1) & 1) ^ 1)) {
+            tc_fence_after_sync();
+            const uint64_t dq = make_smem_desc_sw128(smem_u32(sm.q[qb]));
+            const uint64_t dk = make_smem_desc_sw128(smem_u32(sm.k[st]));
+            const uint32_t d = tmem_base + kColS + b * 64;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) mma_ss(d, dq + (k * 32 >> 4), dk + (k * 32 >> 4), idesc_s, k ? 1u : 0u);
+            tc_commit(&sm.k_empty[st]);
+            tc_commit(&sm.s_full[b]);
+            TRACE(5, s_g)
+            ++s_g;
+            if (++s_j == s_n) {
+              tc_commit(&sm.q_empty[qb]);
+              ++s_itn;
+              ++s_item;
+              s_j = 0;
+              next_s_item();
+            }
+            progress = true;
+          }
+        }
         if (k_item < item_end) {
           const int qb = k_itn & 1;
           if (!q_loaded && mbar_test_wait(&sm.q_empty[qb], ((k_itn >> 1) & 1) ^ 1)) {
@@ -228,6 +282,7 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             sm.mask_ring[k_g % kMaskRing] = e & 3;
             mbar_arrive_expect_tx(&sm.k_full[s], kTileBytes);
             tma_load_2d(sm.k[s], &map_k, 0, ki.kv_row0 + (e >> 2) * 64, &sm.k_full[s]);
+            TRACE(1, k_g)
             ++k_g;
             if (++k_j == ki.n_entries) {
               ++k_item;
@@ -245,6 +300,7 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             const int e = entries[vi.entry_off + v_j];
             mbar_arrive_expect_tx(&sm.v_full[s], kTileBytes);
             tma_load_2d(sm.v[s], &map_v, 0, vi.kv_row0 + (e >> 2) * 64, &sm.v_full[s]);
+            TRACE(2, v_g)
             ++v_g;
             if (++v_j == vi.n_entries) {
               ++v_item;
@@ -257,7 +313,7 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         if (progress) {
           idle_since = clock64();
         } else {
-          __nanosleep(100);  // both rings full: stay off the issue slots of the softmax warp on this scheduler
+          __nanosleep(250);  // nothing to do yet (all jobs run entries ahead): leave the issue slots to the softmax warps
           if (clock64() - idle_since > kWaitCycles) {
             *abort_flag = 1;
             atomicCAS(error_flag, 0, 201);
@@ -270,61 +326,31 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   } else if (warp == 5) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc_f16(128, 64, BF16 ? 1 : 0, false);
       constexpr uint32_t idesc_pv = make_idesc_f16(128, 64, BF16 ? 1 : 0, true);
-      // two cursors over the flattened (item, entry) stream: S runs one entry ahead of PV
-      int s_item = item_begin, s_j = 0, s_n = 0;
-      uint32_t s_g = 0, s_itn = 0;
+      // this thread issues the PV MMAs; the S MMAs are issued by the producer thread, so the
+      // two serial issue chains (waits, four MMAs, commits per entry) run side by side
       int pv_item = item_begin, pv_j = 0, pv_n = 0;
       uint32_t pv_g = 0;
       bool ok = true;
       auto skip_empty = [&](int& item, int& n) {
         while (item < item_end && (n = items[item].n_entries) == 0) ++item;
       };
-      skip_empty(s_item, s_n);
       skip_empty(pv_item, pv_n);
-
-      auto issue_s = [&]() -> bool {
-        const int qb = s_itn & 1;
-        if (s_j == 0) {
-          if (!mbar_wait(&sm.q_full[qb], (s_itn >> 1) & 1, ab, 211)) return false;
-        }
-        const int b = s_g & 1;
-        const uint32_t u = s_g >> 1;
-        const int st = s_g % kStagesK;
-        const uint32_t ph = (s_g / kStagesK) & 1;
-        if (!mbar_wait(&sm.k_full[st], ph, ab, 212)) return false;
-        if (!mbar_wait(&sm.s_free[b], (u & 1) ^ 1, ab, 213)) return false;
-        tc_fence_after_sync();
-        const uint64_t dq = make_smem_desc_sw128(smem_u32(sm.q[qb]));
-        const uint64_t dk = make_smem_desc_sw128(smem_u32(sm.k[st]));
-        const uint32_t d = tmem_base + kColS + b * 64;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) mma_ss(d, dq + (k * 32 >> 4), dk + (k * 32 >> 4), idesc_s, k ? 1u : 0u);
-        tc_commit(&sm.k_empty[st]);
-        tc_commit(&sm.s_full[b]);
-        ++s_g;
-        if (++s_j == s_n) {
-          tc_commit(&sm.q_empty[qb]);
-          ++s_itn;
-          ++s_item;
-          s_j = 0;
-          skip_empty(s_item, s_n);
-        }
-        return true;
-      };
       uint32_t pv_itn = 0;
       auto issue_pv = [&]() -> bool {
         const int b = pv_g & 1;
         const uint32_t u = pv_g >> 1;
         const int st = pv_g % kStagesV;
         const uint32_t ph = (pv_g / kStagesV) & 1;
+        TRACE(6, pv_g)
         if (!mbar_wait(&sm.v_full[st], ph, ab, 214)) return false;
+        TRACE(7, pv_g)
         if (pv_j == 0) {
           // the output tile is overwritten: the softmax warps must have read the previous item's result
           if (!mbar_wait(&sm.o_free, (pv_itn & 1) ^ 1, ab, 215)) return false;
         }
         if (!mbar_wait(&sm.p_full[b], u & 1, ab, 216)) return false;
+        TRACE(8, pv_g)
         tc_fence_after_sync();
         const uint64_t dv = make_smem_desc_sw128(smem_u32(sm.v[st]));
         const uint32_t d = tmem_base + kColO;
@@ -333,6 +359,7 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         for (int k = 0; k < 4; ++k) mma_ts(d, a + k * 8, dv + (k * 2048 >> 4), idesc_pv, (pv_j | k) ? 1u : 0u);
         tc_commit(&sm.v_empty[st]);
         tc_commit(&sm.pv_done[b]);
+        TRACE(9, pv_g)
         ++pv_g;
         if (++pv_j == pv_n) {
           ++pv_item;
@@ -343,11 +370,7 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         return true;
       };
 
-      if (s_item < item_end) ok = issue_s();
-      while (ok && pv_item < item_end) {
-        if (s_item < item_end) ok = issue_s();
-        if (ok) ok = issue_pv();
-      }
+      while (ok && pv_item < item_end) ok = issue_pv();
     }
   } else {
     // ------------------------------------------------------------------ softmax warps 0..3
@@ -370,7 +393,9 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         const int b = gj & 1;
         const uint32_t u = gj >> 1;
         PROF_MARK(0)
+        TRACE(10, gj)
         if (!mbar_wait(&sm.s_full[b], u & 1, ab, 221)) { ok = false; break; }
+        TRACE(11, gj)
         PROF_MARK(1)
         tc_fence_after_sync();
         // the producer published this entry's mask before it loaded the K block of the S tile just waited for
@@ -383,6 +408,7 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         }
         tc_fence_before_sync();
         mbar_arrive(&sm.s_free[b]);
+        TRACE(12, gj)
         PROF_MARK(2)
         float alpha = 1.f;
         bool fix = false;
@@ -410,7 +436,9 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         // the probability buffer was last read by the PV MMA two entries back
         if (gj >= 2) {
           PROF_MARK(3)
+          TRACE(13, gj)
           if (!mbar_wait(&sm.pv_done[b], ((gj - 2) >> 1) & 1, ab, 222)) { ok = false; break; }
+          TRACE(14, gj)
           PROF_MARK(4)
         }
         if (__any_sync(0xffffffffu, fix)) {
@@ -461,9 +489,11 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           tmem_st16(lane_base + kColP + b * 32 + 16, p);
         }
         PROF_MARK(5)
+        TRACE(15, gj)
         tc_wait_st();
         tc_fence_before_sync();
         mbar_arrive(&sm.p_full[b]);
+        TRACE(16, gj)
         PROF_MARK(6)
       }
       if (!ok) break;
@@ -472,7 +502,9 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       {
         const uint32_t gl = g - 1;
         PROF_MARK(0)
+        TRACE(17, gl)
         if (!mbar_wait(&sm.pv_done[gl & 1], (gl >> 1) & 1, ab, 224)) { ok = false; break; }
+        TRACE(18, gl)
         PROF_MARK(7)
         tc_fence_after_sync();
       }
@@ -502,6 +534,7 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           }
         }
       }
+      TRACE(19, g)
       ++itn;
     }
     (void)itn;
@@ -660,6 +693,14 @@ extern "C" rt_status rt_sparse_attention(void* ctx, const void* q, const void* k
                                  static_cast<cudaStream_t>(stream));
 }
 
+#ifdef RT_ATTN_TRACE
+extern "C" rt_status rt_attn_trace_read(unsigned long long* out, int reset) {
+  RT_CHECK_CUDA(cudaDeviceSynchronize());
+  RT_CHECK_CUDA(cudaMemcpyFromSymbol(out, rt::g_trace, sizeof(unsigned long long) * 2 * 8 * 1024));
+  if (reset) RT_CHECK_CUDA(cudaMemset([] { void* p; cudaGetSymbolAddress(&p, rt::g_trace); return p; }(), 0, sizeof(unsigned long long) * 2 * 8 * 1024));
+  return RT_OK;
+}
+#endif
 #ifdef RT_ATTN_PROFILE
 // Tuning builds only: read (and optionally clear) the phase-clock table.
 extern "C" rt_status rt_attn_cta_log_read(unsigned long long* out, int n_ctas) {
