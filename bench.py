@@ -108,6 +108,25 @@ class ClockSampler:
                 "reasons": sorted(self.reasons), "samples": len(self.sm)}
 
 
+def ncu_traffic(kernel, units_here):
+    """DRAM bytes per launch of the dominant kernel from the committed ncu summary
+    (profiles/ncu_<kernel>_microbench.md: dram__bytes_read.sum + dram__bytes_write.sum of one captured
+    launch), scaled to this run's launch by the algorithmic work ratio.  None when no summary exists."""
+    import re
+    path = os.path.join(ROOT, "profiles", f"ncu_{kernel}_microbench.md")
+    ref_units = {"gemm": 2.0 * 16384 * 3072 * 768, "attention": 1048576.0 * 59712}[kernel]
+    try:
+        text = open(path).read()
+        vals = []
+        for key in ("dram__bytes_read.sum", "dram__bytes_write.sum"):
+            m = re.search(r"`" + re.escape(key) + r"`\) \| ([0-9.]+) \| (\w+)", text)
+            scale = {"byte": 1.0, "Kbyte": 1e3, "Mbyte": 1e6, "Gbyte": 1e9}[m.group(2)]
+            vals.append(float(m.group(1)) * scale)
+        return sum(vals) * units_here / ref_units
+    except Exception:
+        return None
+
+
 def flops_per_step(w, lens, visits_per_head):
     T = sum(lens)
     gemm = w["layers"] * T * (8 * w["hidden"] ** 2 + 4 * w["hidden"] * w["ffn"])
@@ -273,16 +292,18 @@ def run_gpu(args, w):
     if dominant_is_gemm:
         roof = {"kernel": "gemm_kernel (tcgen05 projection GEMMs, 4 per layer)", "bound": "tensor",
                 "achieved": gemm_tf, "peak": pk["tf_sustained"], "unit": "TFLOP/s",
-                "frac": gemm_tf / pk["tf_sustained"], "traffic": None,
+                "frac": gemm_tf / pk["tf_sustained"], "traffic": ncu_traffic("gemm", gemm_fl / n_gemm),
                 "launches_per_step": n_gemm, "avg_launch_ms": gemm_ms / n_gemm,
                 "flops_per_launch": gemm_fl / n_gemm}
     else:
         roof = {"kernel": "sparse_attention_kernel (tcgen05 block-sparse attention, 1 per layer)", "bound": "tensor",
                 "achieved": attn_tf, "peak": pk["tf_sustained"], "unit": "TFLOP/s",
-                "frac": attn_tf / pk["tf_sustained"], "traffic": None,
+                "frac": attn_tf / pk["tf_sustained"], "traffic": ncu_traffic("attention", attn_fl / w["layers"]),
                 "launches_per_step": w["layers"], "avg_launch_ms": attn_ms / w["layers"],
                 "flops_per_launch": attn_fl / w["layers"]}
     roof["peak_source"] = pk["source"] + " (sustained bf16 dense, kernel timed inside a long step)"
+    roof["traffic_source"] = ("ncu capture of the same kernel on the micro-benchmark shape (profiles/), "
+                              "scaled by algorithmic work per launch")
 
     # ---- CPU baseline: oracle on a bounded sample of the same workload -----------------------
     cpu = None
