@@ -4,7 +4,7 @@
 // One CTA per SM walks 128 x BN output tiles.  Warp 0 streams A and W k-slices
 // (64 elements = one 128-byte swizzle atom) into a shared-memory ring with TMA;
 // warp 1 issues tcgen05.mma (M=128, N=BN, K=16) into one of two TMEM
-// accumulators; warps 2-5 drain the other accumulator (tcgen05.ld), apply the
+// accumulators; warps 2-9 drain the other accumulator (tcgen05.ld), apply the
 // epilogue and store, so the epilogue of tile i overlaps the main loop of
 // tile i+1.  Stands in for the cuBLAS calls of layers/kernels/mat_mul.cpp:58-76
 // (which accumulate in fp16; this kernel accumulates in fp32).
@@ -12,6 +12,7 @@
 #include <cuda_fp16.h>
 
 #include <algorithm>
+#include <cstdlib>
 
 #include "common.h"
 #include "device_error.h"
@@ -26,7 +27,8 @@ using namespace ptx;
 
 constexpr int kBM = 128;
 constexpr int kBK = 64;
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 320;      // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue
+constexpr int kEpilogueThreads = 256;  // two warps per TMEM lane quarter, alternating 32-column chunks
 
 template <int BN>
 struct GemmCfg {
@@ -104,7 +106,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&acc_full[a], 1);
-      mbar_init(&acc_empty[a], 128);
+      mbar_init(&acc_empty[a], kEpilogueThreads);
     }
     *cta_abort = 0;
     fence_barrier_init();
@@ -176,8 +178,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       }
     }
   } else {
-    // ------------------------------------------------------------- epilogue warps 2..5
+    // ------------------------------------------------------------- epilogue warps 2..9
     const int quarter = warp & 3;
+    const int chunk0 = (warp - 2) >> 2;  // 0: even 32-column chunks, 1: odd chunks
     const int row_in_tile = quarter * 32 + lane;
     uint32_t tile_it = 0;
     bool ok = true;
@@ -190,7 +193,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       const int row = m0 + row_in_tile;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * BN;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = chunk0; c < BN / 32; c += 2) {
         uint32_t r[32];
         tmem_ld32(taddr + c * 32, r);
         tc_wait_ld();
@@ -319,6 +322,10 @@ extern "C" rt_status rt_gemm(void* c, const void* a, const void* w, const void* 
   int bn = 64;
   if (N % 256 == 0 && mt * (N / 256) >= sms) bn = 256;
   else if (N % 128 == 0 && mt * (N / 128) >= sms) bn = 128;
+  if (const char* f = getenv("RAPTOR_B200_GEMM_BN")) {  // tuning override
+    const int v = atoi(f);
+    if ((v == 64 || v == 128 || v == 256) && N % v == 0) bn = v;
+  }
   const bool bf = dtype == RT_BF16;
   if (bn == 256) return bf ? launch_epi<256, true>(c, a, w, bias, M, N, K, epilogue, st)
                            : launch_epi<256, false>(c, a, w, bias, M, N, K, epilogue, st);
