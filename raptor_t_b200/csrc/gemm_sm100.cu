@@ -16,6 +16,7 @@
 
 #include "common.h"
 #include "device_error.h"
+#include "gemm_epilogue.cuh"
 #include "launch_count.h"
 #include "sm100_ptx.cuh"
 #include "tma_host.h"
@@ -24,6 +25,7 @@ namespace rt {
 namespace {
 
 using namespace ptx;
+using namespace gemm_detail;
 
 constexpr int kBM = 128;
 constexpr int kBK = 64;
@@ -39,46 +41,6 @@ struct GemmCfg {
   static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;  // power of two: 128, 256, 512
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
 };
-
-__device__ __forceinline__ float gelu_tanh_f(float x) {
-  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-  float t;
-  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
-  return 0.5f * x * (1.0f + t);
-}
-
-template <bool BF16>
-__device__ __forceinline__ uint32_t pack2(float a, float b) {
-  if constexpr (BF16) {
-    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&h);
-  } else {
-    __half2 h = __floats2half2_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&h);
-  }
-}
-template <bool BF16>
-__device__ __forceinline__ float2 unpack2(uint32_t w) {
-  if constexpr (BF16) {
-    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
-  } else {
-    return __half22float2(*reinterpret_cast<__half2*>(&w));
-  }
-}
-
-// Extra arguments of the QKV epilogue: the [T][3H] result is never written; each
-// 64-wide head slice of a row goes, with bias added (and the query scaled), straight to
-// the per-sequence head-major q / k / v buffers the attention kernel reads
-// (row (seq_first_token*heads + head*seq_len + token_in_seq) of a [T*heads][64] matrix).
-struct QkvEpilogue {
-  uint16_t* q;
-  uint16_t* k;
-  uint16_t* v;
-  const int2* block_seq;  // per packed 64-token block: {first token of its sequence, sequence length}
-  int heads;
-  float q_scale;
-};
-constexpr int kEpiQkv = 3;
 
 template <int BN, bool BF16, int EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -192,58 +154,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       tc_fence_after_sync();
       const int row = m0 + row_in_tile;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * BN;
-#pragma unroll 1
-      for (int c = chunk0; c < BN / 32; c += 2) {
-        uint32_t r[32];
-        tmem_ld32(taddr + c * 32, r);
-        tc_wait_ld();
-        uint32_t o[16];
-        if constexpr (EPI == RT_EPI_NONE) {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) o[j] = pack2<BF16>(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
-        } else {
-          const uint4* bv = reinterpret_cast<const uint4*>(bias + n0 + c * 32);
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const uint4 b4 = __ldg(bv + q);
-            const uint32_t bw[4] = {b4.x, b4.y, b4.z, b4.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 bb = unpack2<BF16>(bw[j]);
-              float x0 = __uint_as_float(r[q * 8 + 2 * j]) + bb.x;
-              float x1 = __uint_as_float(r[q * 8 + 2 * j + 1]) + bb.y;
-              if constexpr (EPI == RT_EPI_BIAS_GELU) {
-                x0 = gelu_tanh_f(x0);
-                x1 = gelu_tanh_f(x1);
-              }
-              if constexpr (EPI == kEpiQkv) {
-                if (n0 + c * 32 < qkv.heads * 64) {  // query part
-                  x0 *= qkv.q_scale;
-                  x1 *= qkv.q_scale;
-                }
-              }
-              o[q * 4 + j] = pack2<BF16>(x0, x1);
-            }
-          }
-        }
-        if (row < M) {
-          uint16_t* dst;
-          if constexpr (EPI == kEpiQkv) {
-            const int hidden = qkv.heads * 64;
-            const int n = n0 + c * 32;
-            const int part = n / hidden;
-            const int hcol = n - part * hidden;
-            const int2 bs = __ldg(qkv.block_seq + (row >> 6));
-            const size_t drow = static_cast<size_t>(bs.x) * qkv.heads + static_cast<size_t>(hcol >> 6) * bs.y +
-                                (row - bs.x);
-            dst = (part == 0 ? qkv.q : part == 1 ? qkv.k : qkv.v) + drow * 64 + (hcol & 63);
-          } else {
-            dst = C + static_cast<size_t>(row) * N + n0 + c * 32;
-          }
-          st_global_v8(dst, o);
-          st_global_v8(dst + 16, o + 8);
-        }
-      }
+      epilogue_row<BN, BF16, EPI>(taddr, row, n0, chunk0, M, N, C, bias, qkv);
       tc_fence_before_sync();
       mbar_arrive(&acc_empty[a]);
     }
@@ -300,6 +211,20 @@ rt_status launch_epi(void* c, const void* a, const void* w, const void* bias, in
 
 }  // namespace
 
+rt_status gemm_pair_dispatch(void* c, const void* a, const void* w, const void* bias, int M, int N, int K, int epi,
+                             bool bf16, cudaStream_t st, const gemm_detail::QkvEpilogue& qkv);
+
+// 256 x 256 CTA-pair tiles pay off when there are enough of them to fill the SM pairs.
+static bool use_pair_tiles(int M, int N) {
+  static const int mode = [] {
+    const char* e = getenv("RAPTOR_B200_GEMM_PAIR");  // 0: never, 1 (default): when the pairs fill the GPU, 2: always
+    return e ? atoi(e) : 1;
+  }();
+  if (mode == 0) return false;
+  if (mode == 2) return N % 256 == 0;  // tuning / tests: whenever the shape allows
+  return N % 256 == 0 && ((M + 255) / 256) * (N / 256) >= 74;
+}
+
 }  // namespace rt
 
 using namespace rt;
@@ -316,6 +241,8 @@ extern "C" rt_status rt_gemm(void* c, const void* a, const void* w, const void* 
   RT_REQUIRE(dtype == RT_F16 || dtype == RT_BF16, RT_ERR_INVALID, "gemm: unknown dtype %d", dtype);
   if (M == 0) return RT_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (use_pair_tiles(M, N))
+    return gemm_pair_dispatch(c, a, w, bias, M, N, K, epilogue, dtype == RT_BF16, st, gemm_detail::QkvEpilogue{});
   // largest tile width that divides N and still gives every SM a tile; else the narrowest
   const int sms = 148;
   const int mt = (M + kBM - 1) / kBM;
@@ -351,6 +278,7 @@ extern "C" rt_status rt_gemm_qkv(void* q, void* k, void* v, const void* a, const
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   QkvEpilogue e{(uint16_t*)q, (uint16_t*)k, (uint16_t*)v, reinterpret_cast<const int2*>(block_seq_dev), heads,
                 q_scale};
+  if (use_pair_tiles(M, N)) return gemm_pair_dispatch(nullptr, a, w, bias, M, N, K, kEpiQkv, dtype == RT_BF16, st, e);
   const int mt = (M + kBM - 1) / kBM;
   // tile width must divide 3*heads*64 and keep a 32-column chunk inside one head: 64, 128 and 256 all do
   const bool wide = N % 256 == 0 && mt * (N / 256) >= 148;
