@@ -40,6 +40,7 @@
 #include "attention.h"
 #include "common.h"
 #include "device_error.h"
+#include "launch.h"
 #include "launch_count.h"
 #include "sm100_ptx.cuh"
 #include "tma_host.h"
@@ -153,6 +154,7 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                         const __grid_constant__ CUtensorMap map_v, uint16_t* __restrict__ ctx,
                         const AttnItem* __restrict__ items, const int32_t* __restrict__ entries,
                         const int32_t* __restrict__ cta_ptr, int hidden, float scale_log2, int* error_flag) {
+  RT_PDL_LAUNCH_DEPENDENTS();
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
   const int warp = threadIdx.x >> 5;
@@ -192,6 +194,7 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   tc_fence_after_sync();
   const uint32_t tmem_base = sm.tmem_slot;
   AbortCtx ab{&sm.abort_flag, error_flag};
+  RT_PDL_WAIT();  // q/k/v, the work list and the output buffer belong to earlier work until here
 
   const int item_begin = cta_ptr[blockIdx.x];
   const int item_end = cta_ptr[blockIdx.x + 1];
@@ -583,9 +586,8 @@ rt_status launch_sparse_attention(void* ctx, const void* q, const void* k, const
                                          cudaSharedmemCarveoutMaxShared));
       set = true;
     }
-    sparse_attention_kernel<true><<<n_ctas, kThreads, kSmemBytes, st>>>(mq, mk, mv, (uint16_t*)ctx, items_dev,
-                                                                         entries_dev, cta_ptr_dev, hidden, scale_log2,
-                                                                         err);
+    RT_CHECK_CUDA(launch_kernel(sparse_attention_kernel<true>, dim3(n_ctas), dim3(kThreads), kSmemBytes, st, mq, mk, mv,
+                                (uint16_t*)ctx, items_dev, entries_dev, cta_ptr_dev, hidden, scale_log2, err));
   } else {
     static bool set = false;
     if (!set) {
@@ -595,9 +597,8 @@ rt_status launch_sparse_attention(void* ctx, const void* q, const void* k, const
                                          cudaSharedmemCarveoutMaxShared));
       set = true;
     }
-    sparse_attention_kernel<false><<<n_ctas, kThreads, kSmemBytes, st>>>(mq, mk, mv, (uint16_t*)ctx, items_dev,
-                                                                          entries_dev, cta_ptr_dev, hidden, scale_log2,
-                                                                          err);
+    RT_CHECK_CUDA(launch_kernel(sparse_attention_kernel<false>, dim3(n_ctas), dim3(kThreads), kSmemBytes, st, mq, mk, mv,
+                                (uint16_t*)ctx, items_dev, entries_dev, cta_ptr_dev, hidden, scale_log2, err));
   }
   count_launch();
   RT_CHECK_CUDA(cudaGetLastError());

@@ -11,6 +11,7 @@
 #include <cuda_runtime.h>
 
 #include "common.h"
+#include "launch.h"
 #include "launch_count.h"
 
 namespace rt {
@@ -68,23 +69,34 @@ __device__ __forceinline__ float warp_sum(float v) {
 // residual + bias + LayerNorm: one warp per row, NV 128-bit vectors per lane.
 // Two-pass statistics on the register copy (mean, then sum of squared
 // deviations), fp32 throughout.  Warps walk rows with a grid stride; bias, gamma
-// and beta are re-read per row from L1 so that the kernel keeps few registers
-// and many warps (loads in flight) per SM.
+// and beta are staged once per CTA in shared memory so that the kernel keeps few
+// registers and many warps (loads in flight) per SM.
 // ---------------------------------------------------------------------------
 template <typename T, int NV>
 __global__ void __launch_bounds__(256, (NV <= 4 ? 3 : 2))
 layernorm_kernel(T* __restrict__ out, const T* __restrict__ x, const T* __restrict__ bias,
                  const T* __restrict__ residual, const T* __restrict__ gamma, const T* __restrict__ beta, int rows,
                  int hidden, float eps) {
+  // bias, gamma and beta sit in shared memory: re-read per row at shared-memory latency
+  // without holding registers across rows
+  extern __shared__ uint4 s_par[];  // [3][hidden / 8]
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
   const int warp = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
   const int total_warps = gridDim.x * warps_per_block;
   const int vecs = hidden >> 3;
   const float inv_h = 1.0f / static_cast<float>(hidden);
-  const uint4* gv = reinterpret_cast<const uint4*>(gamma);
-  const uint4* bv = reinterpret_cast<const uint4*>(beta);
-  const uint4* biv = reinterpret_cast<const uint4*>(bias);
+  RT_PDL_LAUNCH_DEPENDENTS();
+  uint4* s_bias = s_par;
+  uint4* s_gamma = s_par + vecs;
+  uint4* s_beta = s_par + 2 * vecs;
+  for (int i = threadIdx.x; i < vecs; i += blockDim.x) {
+    s_bias[i] = bias ? reinterpret_cast<const uint4*>(bias)[i] : make_uint4(0, 0, 0, 0);
+    s_gamma[i] = reinterpret_cast<const uint4*>(gamma)[i];
+    s_beta[i] = reinterpret_cast<const uint4*>(beta)[i];
+  }
+  __syncthreads();
+  RT_PDL_WAIT();
 
   for (int row = warp; row < rows; row += total_warps) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * hidden);
@@ -104,18 +116,13 @@ layernorm_kernel(T* __restrict__ out, const T* __restrict__ x, const T* __restri
     for (int i = 0; i < NV; ++i) {
       const int c = lane + 32 * i;
       if (c < vecs) {
-        float a[8], r[8];
+        float a[8], r[8], bb[8];
         Vec8<T>::unpack(xv[i], a);
         Vec8<T>::unpack(rv[i], r);
-        if (biv) {
-          float bb[8];
-          Vec8<T>::unpack(__ldg(biv + c), bb);
-#pragma unroll
-          for (int k = 0; k < 8; ++k) a[k] += bb[k];
-        }
+        Vec8<T>::unpack(s_bias[c], bb);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          v[i][k] = a[k] + r[k];
+          v[i][k] = a[k] + bb[k] + r[k];
           sum += v[i][k];
         }
       } else {
@@ -143,8 +150,8 @@ layernorm_kernel(T* __restrict__ out, const T* __restrict__ x, const T* __restri
       const int c = lane + 32 * i;
       if (c < vecs) {
         float gg[8], be[8], o[8];
-        Vec8<T>::unpack(__ldg(gv + c), gg);
-        Vec8<T>::unpack(__ldg(bv + c), be);
+        Vec8<T>::unpack(s_gamma[c], gg);
+        Vec8<T>::unpack(s_beta[c], be);
 #pragma unroll
         for (int k = 0; k < 8; ++k) o[k] = (v[i][k] - mean) * rstd * gg[k] + be[k];
         orow[c] = Vec8<T>::pack(o);
@@ -166,6 +173,8 @@ __device__ __forceinline__ float gelu_tanh(float x) {
 template <typename T, int UNROLL>
 __global__ void __launch_bounds__(256) bias_gelu_kernel(T* __restrict__ x, const T* __restrict__ bias,
                                                         size_t total_vecs, int vecs_per_row) {
+  RT_PDL_LAUNCH_DEPENDENTS();
+  RT_PDL_WAIT();
   const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
   size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   uint4* xv = reinterpret_cast<uint4*>(x);
@@ -207,6 +216,8 @@ __global__ void __launch_bounds__(256) qkv_transpose_kernel(const T* __restrict_
                                                             T* __restrict__ q, T* __restrict__ k, T* __restrict__ v,
                                                             const int32_t* __restrict__ seq_prefix, int n_seq,
                                                             int heads, float q_scale) {
+  RT_PDL_LAUNCH_DEPENDENTS();
+  RT_PDL_WAIT();
   const int blk = blockIdx.x;   // packed 64-token block
   const int part = blockIdx.y;  // 0 q, 1 k, 2 v
   __shared__ int s_first_blk, s_nblk;
@@ -262,6 +273,8 @@ __global__ void __launch_bounds__(256) embeddings_kernel(T* __restrict__ out, co
                                                          const float* __restrict__ type, const float* __restrict__ gamma,
                                                          const float* __restrict__ beta, int tokens, int hidden,
                                                          float eps) {
+  RT_PDL_LAUNCH_DEPENDENTS();
+  RT_PDL_WAIT();
   const int lane = threadIdx.x & 31;
   const int warp = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (warp >= tokens) return;
@@ -342,8 +355,9 @@ static rt_status layernorm_launch(void* out, const void* x, const void* bias, co
   if (blocks < 1) blocks = 1;
 #define RT_LN_CASE(NV)                                                                                           \
   case NV:                                                                                                       \
-    layernorm_kernel<T, NV><<<blocks, threads, 0, st>>>((T*)out, (const T*)x, (const T*)bias, (const T*)residual, \
-                                                        (const T*)gamma, (const T*)beta, rows, hidden, eps);     \
+    launch_kernel(layernorm_kernel<T, NV>, dim3(blocks), dim3(threads), 3 * (hidden / 8) * sizeof(uint4), st,   \
+                  (T*)out, (const T*)x, (const T*)bias, (const T*)residual, (const T*)gamma, (const T*)beta, rows, \
+                  hidden, eps);                                                                                  \
     break;
   switch (nv) {
     RT_LN_CASE(1)
@@ -394,10 +408,11 @@ extern "C" rt_status rt_bias_gelu(void* x, const void* bias, int rows, int cols,
   if (blocks < 1) blocks = 1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == RT_F16)
-    bias_gelu_kernel<__half, UNROLL><<<blocks, threads, 0, st>>>((__half*)x, (const __half*)bias, total, cols / 8);
+    launch_kernel(bias_gelu_kernel<__half, UNROLL>, dim3(blocks), dim3(threads), 0, st, (__half*)x,
+                  (const __half*)bias, total, cols / 8);
   else if (dtype == RT_BF16)
-    bias_gelu_kernel<__nv_bfloat16, UNROLL>
-        <<<blocks, threads, 0, st>>>((__nv_bfloat16*)x, (const __nv_bfloat16*)bias, total, cols / 8);
+    launch_kernel(bias_gelu_kernel<__nv_bfloat16, UNROLL>, dim3(blocks), dim3(threads), 0, st, (__nv_bfloat16*)x,
+                  (const __nv_bfloat16*)bias, total, cols / 8);
   else
     return fail(RT_ERR_INVALID, "bias_gelu: unknown dtype %d", dtype);
   count_launch();
@@ -416,12 +431,12 @@ extern "C" rt_status rt_qkv_bias_transpose(const void* qkv, const void* bias, vo
   dim3 grid(total_blocks, 3);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == RT_F16)
-    qkv_transpose_kernel<__half><<<grid, 256, 0, st>>>((const __half*)qkv, (const __half*)bias, (__half*)q, (__half*)k,
-                                                       (__half*)v, seq_block_prefix_dev, n_seq, heads, q_scale);
+    launch_kernel(qkv_transpose_kernel<__half>, grid, dim3(256), 0, st, (const __half*)qkv, (const __half*)bias,
+                  (__half*)q, (__half*)k, (__half*)v, seq_block_prefix_dev, n_seq, heads, q_scale);
   else if (dtype == RT_BF16)
-    qkv_transpose_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
-        (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)bias, (__nv_bfloat16*)q, (__nv_bfloat16*)k, (__nv_bfloat16*)v,
-        seq_block_prefix_dev, n_seq, heads, q_scale);
+    launch_kernel(qkv_transpose_kernel<__nv_bfloat16>, grid, dim3(256), 0, st, (const __nv_bfloat16*)qkv,
+                  (const __nv_bfloat16*)bias, (__nv_bfloat16*)q, (__nv_bfloat16*)k, (__nv_bfloat16*)v,
+                  seq_block_prefix_dev, n_seq, heads, q_scale);
   else
     return fail(RT_ERR_INVALID, "qkv_transpose: unknown dtype %d", dtype);
   count_launch();
@@ -443,9 +458,9 @@ extern "C" rt_status rt_embeddings(void* out, const int32_t* ids, const int32_t*
   const int blocks = (tokens + wpb - 1) / wpb;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 #define RT_EMB(T, NV)                                                                                          \
-  embeddings_kernel<T, NV><<<blocks, threads, 0, st>>>((T*)out, ids, pos_ids, type_ids, (const float*)word,   \
-                                                       (const float*)pos, (const float*)type, (const float*)gamma, \
-                                                       (const float*)beta, tokens, hidden, eps)
+  launch_kernel(embeddings_kernel<T, NV>, dim3(blocks), dim3(threads), 0, st, (T*)out, ids, pos_ids, type_ids, \
+                (const float*)word, (const float*)pos, (const float*)type, (const float*)gamma,                \
+                (const float*)beta, tokens, hidden, eps)
   if (dtype == RT_F16) {
     switch (nv) { case 1: RT_EMB(__half, 1); break; case 2: RT_EMB(__half, 2); break; case 3: RT_EMB(__half, 3); break; default: RT_EMB(__half, 4); }
   } else if (dtype == RT_BF16) {

@@ -16,6 +16,7 @@
 #include "common.h"
 #include "device_error.h"
 #include "gemm_epilogue.cuh"
+#include "launch.h"
 #include "launch_count.h"
 #include "sm100_ptx.cuh"
 #include "tma_host.h"
@@ -51,6 +52,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+  RT_PDL_LAUNCH_DEPENDENTS();
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -78,6 +80,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   cluster_arrive();  // the peer's barriers exist before anything remote touches them
   cluster_wait();
   tc_fence_after_sync();
+  RT_PDL_WAIT();  // operands and the output buffer belong to the previous kernel until here
   const uint32_t tmem_base = *tmem_slot;
   AbortCtx ab{cta_abort, error_flag};
 
@@ -186,7 +189,8 @@ rt_status launch_pair(void* c, const void* a, const void* w, const void* bias, i
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int tiles = ((M + kTileM - 1) / kTileM) * (N / kTileN);
   const int pairs = std::min(tiles, sms / 2);
-  kern<<<2 * pairs, kThreads, kSmemBytes, st>>>(ma, mw, (uint16_t*)c, (const uint16_t*)bias, M, N, K, err, qkv);
+  RT_CHECK_CUDA(launch_kernel(kern, dim3(2 * pairs), dim3(kThreads), kSmemBytes, st, ma, mw, (uint16_t*)c,
+                              (const uint16_t*)bias, M, N, K, err, qkv));
   count_launch();
   RT_CHECK_CUDA(cudaGetLastError());
   return RT_OK;

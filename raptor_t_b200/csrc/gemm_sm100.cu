@@ -17,6 +17,7 @@
 #include "common.h"
 #include "device_error.h"
 #include "gemm_epilogue.cuh"
+#include "launch.h"
 #include "launch_count.h"
 #include "sm100_ptx.cuh"
 #include "tma_host.h"
@@ -58,6 +59,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+  RT_PDL_LAUNCH_DEPENDENTS();
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
@@ -80,6 +82,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
+  RT_PDL_WAIT();  // operands and the output buffer belong to the previous kernel until here
   const uint32_t tmem_base = *tmem_slot;
   AbortCtx ab{cta_abort, error_flag};
 
@@ -192,7 +195,8 @@ rt_status launch(void* c, const void* a, const void* w, const void* bias, int M,
   RT_REQUIRE(err != nullptr, RT_ERR_CUDA, "gemm: cannot allocate the device error word");
   const int tiles = ((M + kBM - 1) / kBM) * (N / BN);
   const int grid = std::min(tiles, gemm_sm_count());
-  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, st>>>(ma, mw, (uint16_t*)c, (const uint16_t*)bias, M, N, K, err, qkv);
+  RT_CHECK_CUDA(launch_kernel(kern, dim3(grid), dim3(kGemmThreads), Cfg::kSmemBytes, st, ma, mw, (uint16_t*)c,
+                              (const uint16_t*)bias, M, N, K, err, qkv));
   count_launch();
   RT_CHECK_CUDA(cudaGetLastError());
   return RT_OK;
