@@ -34,6 +34,8 @@ enum {
 enum { RT_F16 = 0, RT_BF16 = 1 };
 enum { RT_PATTERN_BIGBIRD = 0, RT_PATTERN_BAND = 1 };
 enum { RT_EPI_NONE = 0, RT_EPI_BIAS = 1, RT_EPI_BIAS_GELU = 2 };
+/* (3 is the internal QKV scatter of rt_gemm_qkv) */
+enum { RT_EPI_BIAS_RESIDUAL = 4 };  /* C = A W^T + bias + residual (rt_gemm_residual) */
 
 /* Model shape.  Replaces the constants hard-coded in layers/bert_attention.h:37-40
  * (12 heads, 768, block 64), layers/tensor_set.h:40-44 and layers/bert_output.cpp:23 (eps). */
@@ -126,6 +128,12 @@ rt_status rt_embeddings(void* out_dev, const int32_t* ids_dev, const int32_t* po
  * layers/kernels/mat_mul.cpp:9-96 (MatMul; note W here is [out][in], i.e. B transposed). */
 rt_status rt_gemm(void* c_dev, const void* a_dev, const void* w_dev, const void* bias_dev, int M, int N,
                   int K, int epilogue, int dtype, void* stream);
+
+/* C[M][N] = A W^T + bias + residual[M][N]: the pre-LayerNorm sum of the attention-output and
+ * FFN-down projections, so that the LayerNorm that follows reads one tensor instead of two
+ * (layers/multi_headed_attention.cpp:206-210, layers/bert_output.cpp:19-23).  C may alias residual. */
+rt_status rt_gemm_residual(void* c_dev, const void* a_dev, const void* w_dev, const void* bias_dev,
+                           const void* residual_dev, int M, int N, int K, int dtype, void* stream);
 
 /* Fused QKV projection: (A[M][K] * W[3*heads*64][K]^T + bias), query part scaled by q_scale,
  * written head-major per sequence straight into q/k/v (the layout of rt_qkv_bias_transpose) -
@@ -241,7 +249,9 @@ rt_status rt_encoder_get_timing(rt_encoder* enc, const char* key, float* ms_out)
 rt_status rt_encoder_enable_timing(rt_encoder* enc, int on);
 rt_status rt_encoder_kernel_launches(rt_encoder* enc, int64_t* launches_out);
 /* options: "fuse_gelu" (1: bias+GELU in the FFN-up GEMM epilogue, 0: separate rt_bias_gelu kernel);
- * "fuse_qkv" (1: rt_gemm_qkv, 0: rt_gemm + rt_qkv_bias_transpose).  Both default to 1. */
+ * "fuse_qkv" (1: rt_gemm_qkv, 0: rt_gemm + rt_qkv_bias_transpose); "fuse_residual" (1: bias + residual
+ * added in the projection GEMM's epilogue, LayerNorm reads one tensor; default 0: it costs one more 16-bit
+ * rounding and measured slower).  fuse_gelu and fuse_qkv default to 1. */
 rt_status rt_encoder_set_option(rt_encoder* enc, const char* name, int value);
 /* work-list statistics of one layer of the prepared batch */
 rt_status rt_encoder_plan_stats(rt_encoder* enc, int layer, int64_t* entries_out, int64_t* visits_out,

@@ -117,6 +117,7 @@ struct rt_encoder {
   bool emb_set = false;
   bool fuse_gelu = true;
   bool fuse_qkv = true;
+  bool fuse_residual = false;  // measured slower on B200 (GEMM epilogue cost > LayerNorm saving); kept as an option
 
   // scratch ("TensorSet")
   std::map<std::string, DevBuf> scratch;
@@ -363,11 +364,18 @@ rt_status run_attention(rt_encoder* e, int l, const void* input, void* output, c
                                    reinterpret_cast<const int32_t*>(dev + e->cta_off), e->attn_ctas, T, c.heads, 1.0f, dt,
                                    st));
   }
-  {
-    Span s(e, st, "gemm");
-    RT_TRY(rt_gemm(dense, ctx, w.ao_w.p, nullptr, T, H, H, RT_EPI_NONE, dt, st));
-  }
-  {
+  if (e->fuse_residual) {
+    {
+      Span s(e, st, "gemm");
+      RT_TRY(rt_gemm_residual(dense, ctx, w.ao_w.p, w.ao_b.p, input, T, H, H, dt, st));
+    }
+    Span s(e, st, "add_bias_and_layernorm_kernel");
+    RT_TRY(rt_bias_residual_layernorm(output, dense, nullptr, nullptr, w.aln_g.p, w.aln_b.p, T, H, c.eps, dt, st));
+  } else {
+    {
+      Span s(e, st, "gemm");
+      RT_TRY(rt_gemm(dense, ctx, w.ao_w.p, nullptr, T, H, H, RT_EPI_NONE, dt, st));
+    }
     Span s(e, st, "add_bias_and_layernorm_kernel");
     RT_TRY(rt_bias_residual_layernorm(output, dense, w.ao_b.p, input, w.aln_g.p, w.aln_b.p, T, H, c.eps, dt, st));
   }
@@ -397,6 +405,16 @@ rt_status run_output(rt_encoder* e, int l, const void* ffn, const void* residual
   LayerWeights& w = e->layers[l];
   RT_REQUIRE(w.set, RT_ERR_STATE, "layer %d has no weights", l);
   void* dense = e->scratch["dense_out"].p;
+  if (e->fuse_residual) {
+    {
+      Span s(e, st, "gemm");
+      RT_TRY(rt_gemm_residual(dense, ffn, w.down_w.p, w.down_b.p, residual, e->tokens, c.hidden, c.ffn, c.dtype, st));
+    }
+    Span s(e, st, "add_bias_and_layernorm_kernel");
+    RT_TRY(rt_bias_residual_layernorm(out, dense, nullptr, nullptr, w.oln_g.p, w.oln_b.p, e->tokens, c.hidden, c.eps,
+                                      c.dtype, st));
+    return RT_OK;
+  }
   {
     Span s(e, st, "gemm");
     RT_TRY(rt_gemm(dense, ffn, w.down_w.p, nullptr, e->tokens, c.hidden, c.ffn, RT_EPI_NONE, c.dtype, st));
@@ -521,6 +539,10 @@ extern "C" rt_status rt_encoder_set_option(rt_encoder* e, const char* name, int 
   }
   if (std::strcmp(name, "fuse_qkv") == 0) {
     e->fuse_qkv = value != 0;
+    return RT_OK;
+  }
+  if (std::strcmp(name, "fuse_residual") == 0) {
+    e->fuse_residual = value != 0;
     return RT_OK;
   }
   return fail(RT_ERR_INVALID, "set_option: unknown option '%s'", name);

@@ -66,6 +66,7 @@ __device__ __forceinline__ float2 unpack2(uint32_t w) {
 // the per-sequence head-major q / k / v buffers the attention kernel reads
 // (row (seq_first_token*heads + head*seq_len + token_in_seq) of a [T*heads][64] matrix).
 struct QkvEpilogue {
+  const uint16_t* residual;  // RT_EPI_BIAS_RESIDUAL: [M][N], added after the bias
   uint16_t* q;
   uint16_t* k;
   uint16_t* v;
@@ -85,6 +86,23 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t* r, int c, int row
 #pragma unroll
     for (int j = 0; j < 16; ++j) o[j] = pack2<BF16>(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
   } else {
+    uint32_t res[16];
+    if constexpr (EPI == RT_EPI_BIAS_RESIDUAL) {
+      if (row < M) {
+        const uint4* rp = reinterpret_cast<const uint4*>(qkv.residual + static_cast<size_t>(row) * N + n0 + c * 32);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint4 t = rp[q];
+          res[4 * q] = t.x;
+          res[4 * q + 1] = t.y;
+          res[4 * q + 2] = t.z;
+          res[4 * q + 3] = t.w;
+        }
+      } else {
+#pragma unroll
+        for (int q = 0; q < 16; ++q) res[q] = 0u;
+      }
+    }
     const uint4* bv = reinterpret_cast<const uint4*>(bias + n0 + c * 32);
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
@@ -96,6 +114,11 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t* r, int c, int row
         float x0 = __uint_as_float(r[q * 8 + 2 * j]) + bb.x;
         float x1 = __uint_as_float(r[q * 8 + 2 * j + 1]) + bb.y;
         if constexpr (EPI == RT_EPI_BIAS_GELU) gelu_tanh_f2(x0, x1);
+        if constexpr (EPI == RT_EPI_BIAS_RESIDUAL) {
+          const float2 rr = unpack2<BF16>(res[q * 4 + j]);
+          x0 += rr.x;
+          x1 += rr.y;
+        }
         if constexpr (EPI == kEpiQkv) {
           if (n0 + c * 32 < qkv.heads * 64) {  // query part
             x0 *= qkv.q_scale;

@@ -211,6 +211,9 @@ rt_status gemm_pair_dispatch(void* c, const void* a, const void* w, const void* 
     case RT_EPI_BIAS_GELU:
       return bf16 ? launch_pair<true, RT_EPI_BIAS_GELU>(c, a, w, bias, M, N, K, st, qkv)
                   : launch_pair<false, RT_EPI_BIAS_GELU>(c, a, w, bias, M, N, K, st, qkv);
+    case RT_EPI_BIAS_RESIDUAL:
+      return bf16 ? launch_pair<true, RT_EPI_BIAS_RESIDUAL>(c, a, w, bias, M, N, K, st, qkv)
+                  : launch_pair<false, RT_EPI_BIAS_RESIDUAL>(c, a, w, bias, M, N, K, st, qkv);
     case gemm_detail::kEpiQkv:
       return bf16 ? launch_pair<true, gemm_detail::kEpiQkv>(c, a, w, bias, M, N, K, st, qkv)
                   : launch_pair<false, gemm_detail::kEpiQkv>(c, a, w, bias, M, N, K, st, qkv);

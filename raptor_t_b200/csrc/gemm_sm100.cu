@@ -204,11 +204,12 @@ rt_status launch(void* c, const void* a, const void* w, const void* bias, int M,
 
 template <int BN, bool BF16>
 rt_status launch_epi(void* c, const void* a, const void* w, const void* bias, int M, int N, int K, int epi,
-                     cudaStream_t st) {
+                     cudaStream_t st, const QkvEpilogue& qkv = QkvEpilogue{}) {
   switch (epi) {
     case RT_EPI_NONE: return launch<BN, BF16, RT_EPI_NONE>(c, a, w, bias, M, N, K, st);
     case RT_EPI_BIAS: return launch<BN, BF16, RT_EPI_BIAS>(c, a, w, bias, M, N, K, st);
     case RT_EPI_BIAS_GELU: return launch<BN, BF16, RT_EPI_BIAS_GELU>(c, a, w, bias, M, N, K, st);
+    case RT_EPI_BIAS_RESIDUAL: return launch<BN, BF16, RT_EPI_BIAS_RESIDUAL>(c, a, w, bias, M, N, K, st, qkv);
   }
   return fail(RT_ERR_INVALID, "gemm: unknown epilogue %d", epi);
 }
@@ -233,8 +234,8 @@ static bool use_pair_tiles(int M, int N) {
 
 using namespace rt;
 
-extern "C" rt_status rt_gemm(void* c, const void* a, const void* w, const void* bias, int M, int N, int K, int epilogue,
-                             int dtype, void* stream) {
+static rt_status gemm_entry(void* c, const void* a, const void* w, const void* bias, int M, int N, int K, int epilogue,
+                            int dtype, void* stream, const gemm_detail::QkvEpilogue& extra) {
   RT_REQUIRE(c && a && w, RT_ERR_INVALID, "gemm: null pointer");
   RT_REQUIRE(M >= 0 && N > 0 && K > 0 && N % 64 == 0 && K % 64 == 0, RT_ERR_INVALID,
              "gemm: need N %% 64 == 0 and K %% 64 == 0 (got M=%d N=%d K=%d)", M, N, K);
@@ -246,7 +247,7 @@ extern "C" rt_status rt_gemm(void* c, const void* a, const void* w, const void* 
   if (M == 0) return RT_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (use_pair_tiles(M, N))
-    return gemm_pair_dispatch(c, a, w, bias, M, N, K, epilogue, dtype == RT_BF16, st, gemm_detail::QkvEpilogue{});
+    return gemm_pair_dispatch(c, a, w, bias, M, N, K, epilogue, dtype == RT_BF16, st, extra);
   // largest tile width that divides N and still gives every SM a tile; else the narrowest
   const int sms = 148;
   const int mt = (M + kBM - 1) / kBM;
@@ -258,12 +259,28 @@ extern "C" rt_status rt_gemm(void* c, const void* a, const void* w, const void* 
     if ((v == 64 || v == 128 || v == 256) && N % v == 0) bn = v;
   }
   const bool bf = dtype == RT_BF16;
-  if (bn == 256) return bf ? launch_epi<256, true>(c, a, w, bias, M, N, K, epilogue, st)
-                           : launch_epi<256, false>(c, a, w, bias, M, N, K, epilogue, st);
-  if (bn == 128) return bf ? launch_epi<128, true>(c, a, w, bias, M, N, K, epilogue, st)
-                           : launch_epi<128, false>(c, a, w, bias, M, N, K, epilogue, st);
-  return bf ? launch_epi<64, true>(c, a, w, bias, M, N, K, epilogue, st)
-            : launch_epi<64, false>(c, a, w, bias, M, N, K, epilogue, st);
+  if (bn == 256) return bf ? launch_epi<256, true>(c, a, w, bias, M, N, K, epilogue, st, extra)
+                           : launch_epi<256, false>(c, a, w, bias, M, N, K, epilogue, st, extra);
+  if (bn == 128) return bf ? launch_epi<128, true>(c, a, w, bias, M, N, K, epilogue, st, extra)
+                           : launch_epi<128, false>(c, a, w, bias, M, N, K, epilogue, st, extra);
+  return bf ? launch_epi<64, true>(c, a, w, bias, M, N, K, epilogue, st, extra)
+            : launch_epi<64, false>(c, a, w, bias, M, N, K, epilogue, st, extra);
+}
+
+extern "C" rt_status rt_gemm(void* c, const void* a, const void* w, const void* bias, int M, int N, int K, int epilogue,
+                             int dtype, void* stream) {
+  RT_REQUIRE(epilogue == RT_EPI_NONE || epilogue == RT_EPI_BIAS || epilogue == RT_EPI_BIAS_GELU, RT_ERR_INVALID,
+             "gemm: unknown epilogue %d", epilogue);
+  return gemm_entry(c, a, w, bias, M, N, K, epilogue, dtype, stream, gemm_detail::QkvEpilogue{});
+}
+
+extern "C" rt_status rt_gemm_residual(void* c, const void* a, const void* w, const void* bias, const void* residual,
+                                      int M, int N, int K, int dtype, void* stream) {
+  RT_REQUIRE(residual != nullptr && (reinterpret_cast<uintptr_t>(residual) & 15u) == 0, RT_ERR_INVALID,
+             "gemm_residual: residual must be a 16-byte aligned device pointer");
+  gemm_detail::QkvEpilogue e{};
+  e.residual = static_cast<const uint16_t*>(residual);
+  return gemm_entry(c, a, w, bias, M, N, K, RT_EPI_BIAS_RESIDUAL, dtype, stream, e);
 }
 
 extern "C" rt_status rt_gemm_qkv(void* q, void* k, void* v, const void* a, const void* w, const void* bias,
@@ -280,7 +297,7 @@ extern "C" rt_status rt_gemm_qkv(void* q, void* k, void* v, const void* a, const
   RT_REQUIRE(dtype == RT_F16 || dtype == RT_BF16, RT_ERR_INVALID, "gemm_qkv: unknown dtype %d", dtype);
   if (M == 0) return RT_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  QkvEpilogue e{(uint16_t*)q, (uint16_t*)k, (uint16_t*)v, reinterpret_cast<const int2*>(block_seq_dev), heads,
+  QkvEpilogue e{nullptr, (uint16_t*)q, (uint16_t*)k, (uint16_t*)v, reinterpret_cast<const int2*>(block_seq_dev), heads,
                 q_scale};
   if (use_pair_tiles(M, N)) return gemm_pair_dispatch(nullptr, a, w, bias, M, N, K, kEpiQkv, dtype == RT_BF16, st, e);
   const int mt = (M + kBM - 1) / kBM;

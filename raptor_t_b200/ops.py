@@ -78,6 +78,16 @@ def gemm(a, w, bias=None, epilogue=capi.RT_EPI_NONE, out=None):
     return out
 
 
+def gemm_residual(a, w, bias, residual, out=None):
+    """out[M,N] = a @ w^T + bias + residual (pre-LayerNorm sum); out may alias residual."""
+    M, K = a.shape
+    N = w.shape[0]
+    if out is None:
+        out = torch.empty(M, N, dtype=a.dtype, device=a.device)
+    check(lib.rt_gemm_residual(_p(out), _p(a), _p(w), _p(bias), _p(residual), M, N, K, _dt(a), _stream()))
+    return out
+
+
 def block_seq_table(lens_tokens, device="cuda"):
     """int32 [N, 2]: for every packed 64-token block {first token of its sequence, sequence length}."""
     import numpy as np

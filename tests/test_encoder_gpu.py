@@ -37,6 +37,8 @@ def test_small_encoder_from_ids(dtype, fuse):
     enc = _make(cfg, dtype, P)
     enc.set_option("fuse_gelu", fuse)
     enc.set_option("fuse_qkv", fuse)
+    # the fused residual epilogue rounds the pre-LayerNorm sum to 16 bits: checked in fp16 only
+    enc.set_option("fuse_residual", fuse if dtype == torch.float16 else 0)
     lens = [832, 1024, 512, 64]
     rng = np.random.default_rng(0)
     seqs = [torch.from_numpy(rng.integers(0, cfg.vocab, size=n)).int() for n in lens]

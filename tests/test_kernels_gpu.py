@@ -142,6 +142,22 @@ def test_gemm_qkv_equals_gemm_plus_transpose(ops, dtype, heads, lens):
         t0 += n
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K", [(333, 768, 768), (20032, 768, 3072), (130, 128, 256)])
+def test_gemm_residual(ops, dtype, M, N, K):
+    g = torch.Generator(device="cuda").manual_seed(M)
+    a = torch.randn(M, K, device="cuda", generator=g).to(dtype)
+    w = (torch.randn(N, K, device="cuda", generator=g) / math.sqrt(K)).to(dtype)
+    b = torch.randn(N, device="cuda", generator=g).to(dtype)
+    r = torch.randn(M, N, device="cuda", generator=g).to(dtype)
+    ref = a.float() @ w.float().t() + b.float() + r.float()
+    out = ops.gemm_residual(a, w, b, r)
+    assert (out.float() - ref).abs().max().item() < _tol(dtype) * 4
+    inplace = ops.gemm_residual(a, w, b, r, out=r)   # output over the residual buffer
+    assert torch.equal(inplace, out)
+    ops.check_device()
+
+
 def _attention_case(ops, dtype, cfg, lens, layer, seed):
     from raptor_t_b200 import capi, metadata
     rc = capi.make_config(hidden=cfg.hidden, heads=cfg.heads, ffn=cfg.ffn, layers=cfg.layers, max_pos=cfg.max_pos,
