@@ -35,6 +35,7 @@
 #include <cuda_fp16.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <vector>
 
 #include "attention.h"
@@ -153,7 +154,8 @@ __global__ void __maxnreg__(160)
 sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, uint16_t* __restrict__ ctx,
                         const AttnItem* __restrict__ items, const int32_t* __restrict__ entries,
-                        const int32_t* __restrict__ cta_ptr, int hidden, float scale_log2, int* error_flag) {
+                        const int32_t* __restrict__ cta_ptr, int hidden, float scale_log2, int* error_flag,
+                        float* __restrict__ part_o, float* __restrict__ part_ml) {
   RT_PDL_LAUNCH_DEPENDENTS();
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
@@ -512,8 +514,14 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         tc_fence_after_sync();
       }
       const int tok0 = half == 0 ? item.out_tok0 : item.out_tok1;
-      const float inv = 1.0f / l;
-      uint16_t* dst = ctx + static_cast<size_t>((tok0 >= 0 ? tok0 : 0) + (row & 63)) * hidden + item.head * 64;
+      const int slot = (item.head >> 8) - 1;  // >= 0: this item is one part of a split list
+      const float inv = slot >= 0 ? 1.0f : 1.0f / l;
+      uint16_t* dst = ctx + static_cast<size_t>((tok0 >= 0 ? tok0 : 0) + (row & 63)) * hidden + (item.head & 255) * 64;
+      float* pdst = part_o + (static_cast<size_t>(slot >= 0 ? slot : 0) * 128 + row) * 64;
+      if (slot >= 0 && tok0 >= 0) {
+        float2 ml = make_float2(m_ref, l);
+        *reinterpret_cast<float2*>(part_ml + (static_cast<size_t>(slot) * 128 + row) * 2) = ml;
+      }
 #pragma unroll
       for (int hc = 0; hc < 2; ++hc) {
         uint32_t o[32];
@@ -527,17 +535,22 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           mbar_arrive(&sm.o_free);
         }
         if (tok0 >= 0) {
+          if (slot >= 0) {
+            // un-normalised fp32 partial result (relative to m_ref) for the merge kernel
 #pragma unroll
-          for (int q = 0; q < 2; ++q) {
-            uint32_t w[8];
+            for (int q = 0; q < 4; ++q) st_global_v8(pdst + hc * 32 + 8 * q, o + 8 * q);
+          } else {
 #pragma unroll
-            for (int e = 0; e < 8; ++e)
-              w[e] = pack2<BF16>(__uint_as_float(o[16 * q + 2 * e]) * inv, __uint_as_float(o[16 * q + 2 * e + 1]) * inv);
-            st_global_v8(dst + hc * 32 + 16 * q, w);
+            for (int q = 0; q < 2; ++q) {
+              uint32_t w[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e)
+                w[e] = pack2<BF16>(__uint_as_float(o[16 * q + 2 * e]) * inv, __uint_as_float(o[16 * q + 2 * e + 1]) * inv);
+              st_global_v8(dst + hc * 32 + 16 * q, w);
+            }
           }
         }
       }
-      TRACE(19, g)
       ++itn;
     }
     (void)itn;
@@ -560,11 +573,60 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   }
 }
 
+// Merges the partial results of split lists: one CTA per group, one thread per tile row.
+//   out = sum_i O_i 2^(m_i - M) / sum_i l_i 2^(m_i - M),  M = max_i m_i
+template <bool BF16>
+__global__ void __launch_bounds__(128) merge_partials_kernel(uint16_t* __restrict__ ctx,
+                                                             const int32_t* __restrict__ groups,
+                                                             const float* __restrict__ part_o,
+                                                             const float* __restrict__ part_ml, int hidden) {
+  RT_PDL_LAUNCH_DEPENDENTS();
+  RT_PDL_WAIT();
+  const int32_t* g = groups + blockIdx.x * 6;
+  const int first = g[0], parts = g[1], head = g[4] & 255;
+  const int row = threadIdx.x;
+  const int tok0 = row < 64 ? g[2] : g[3];
+  if (tok0 < 0) return;
+  float M = -INFINITY;
+  for (int i = 0; i < parts; ++i) M = fmaxf(M, part_ml[(static_cast<size_t>(first + i) * 128 + row) * 2]);
+  float L = 0.f;
+  for (int i = 0; i < parts; ++i) {
+    const float2 ml = *reinterpret_cast<const float2*>(part_ml + (static_cast<size_t>(first + i) * 128 + row) * 2);
+    L += ml.y * ex2(ml.x - M);
+  }
+  const float inv = 1.0f / L;
+  uint16_t* dst = ctx + static_cast<size_t>(tok0 + (row & 63)) * hidden + head * 64;
+#pragma unroll 1
+  for (int c = 0; c < 64; c += 16) {
+    float acc[16];
+#pragma unroll
+    for (int k = 0; k < 16; ++k) acc[k] = 0.f;
+    for (int i = 0; i < parts; ++i) {
+      const size_t base = static_cast<size_t>(first + i) * 128 + row;
+      const float w = ex2(part_ml[base * 2] - M);
+      const float4* src = reinterpret_cast<const float4*>(part_o + base * 64 + c);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float4 v = src[q];
+        acc[4 * q] += w * v.x;
+        acc[4 * q + 1] += w * v.y;
+        acc[4 * q + 2] += w * v.z;
+        acc[4 * q + 3] += w * v.w;
+      }
+    }
+    uint32_t o[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) o[k] = pack2<BF16>(acc[2 * k] * inv, acc[2 * k + 1] * inv);
+    st_global_v8(dst + c, o);
+  }
+}
+
 }  // namespace
 
 rt_status launch_sparse_attention(void* ctx, const void* q, const void* k, const void* v, const AttnItem* items_dev,
                                   const int32_t* entries_dev, const int32_t* cta_ptr_dev, int n_ctas,
-                                  int total_tokens, int heads, float scale, int dtype, cudaStream_t st, int* error_word_dev) {
+                                  int total_tokens, int heads, float scale, int dtype, cudaStream_t st, int* error_word_dev,
+                                  const AttnSplit& split) {
   RT_REQUIRE(dtype == RT_F16 || dtype == RT_BF16, RT_ERR_INVALID, "sparse_attention: unknown dtype %d", dtype);
   RT_REQUIRE(n_ctas > 0 && total_tokens > 0 && heads > 0, RT_ERR_INVALID, "sparse_attention: empty plan");
   const uint64_t rows = static_cast<uint64_t>(total_tokens) * heads;
@@ -587,7 +649,8 @@ rt_status launch_sparse_attention(void* ctx, const void* q, const void* k, const
       set = true;
     }
     RT_CHECK_CUDA(launch_kernel(sparse_attention_kernel<true>, dim3(n_ctas), dim3(kThreads), kSmemBytes, st, mq, mk, mv,
-                                (uint16_t*)ctx, items_dev, entries_dev, cta_ptr_dev, hidden, scale_log2, err));
+                                (uint16_t*)ctx, items_dev, entries_dev, cta_ptr_dev, hidden, scale_log2, err,
+                                split.part_o, split.part_ml));
   } else {
     static bool set = false;
     if (!set) {
@@ -598,13 +661,25 @@ rt_status launch_sparse_attention(void* ctx, const void* q, const void* k, const
       set = true;
     }
     RT_CHECK_CUDA(launch_kernel(sparse_attention_kernel<false>, dim3(n_ctas), dim3(kThreads), kSmemBytes, st, mq, mk, mv,
-                                (uint16_t*)ctx, items_dev, entries_dev, cta_ptr_dev, hidden, scale_log2, err));
+                                (uint16_t*)ctx, items_dev, entries_dev, cta_ptr_dev, hidden, scale_log2, err,
+                                split.part_o, split.part_ml));
   }
   count_launch();
   RT_CHECK_CUDA(cudaGetLastError());
+  if (split.n_groups > 0) {
+    RT_REQUIRE(split.groups_dev && split.part_o && split.part_ml, RT_ERR_INVALID,
+               "sparse_attention: split lists without partial-result scratch");
+    if (dtype == RT_BF16)
+      RT_CHECK_CUDA(launch_kernel(merge_partials_kernel<true>, dim3(split.n_groups), dim3(128), 0, st, (uint16_t*)ctx,
+                                  split.groups_dev, (const float*)split.part_o, (const float*)split.part_ml, hidden));
+    else
+      RT_CHECK_CUDA(launch_kernel(merge_partials_kernel<false>, dim3(split.n_groups), dim3(128), 0, st, (uint16_t*)ctx,
+                                  split.groups_dev, (const float*)split.part_o, (const float*)split.part_ml, hidden));
+    count_launch();
+    RT_CHECK_CUDA(cudaGetLastError());
+  }
   return RT_OK;
 }
-
 
 }  // namespace rt
 
@@ -616,7 +691,7 @@ using namespace rt;
 struct rt_attn_plan {
   AttnPlanHost host;
   uint8_t* dev = nullptr;
-  size_t items_off = 0, entries_off = 0, cta_off = 0, bytes = 0;
+  size_t items_off = 0, entries_off = 0, cta_off = 0, groups_off = 0, part_o_off = 0, part_ml_off = 0, bytes = 0;
   int n_ctas = 0;
   int dtype = 0;
 };
@@ -636,7 +711,9 @@ extern "C" rt_status rt_attn_plan_create(const rt_config* cfg, const int32_t* le
   for (int s = 0; s < n_seq; ++s) nblk += lens[s] / cfg->block;
   const int64_t visits = kv_ptr[nblk];
   auto* p = new rt_attn_plan();
-  rt_status s = build_attn_plan(*cfg, lens, n_seq, kv_ptr, kv_idx, visits, n_ctas, p->host);
+  int split = kDefaultSplitEntries;
+  if (const char* e = getenv("RAPTOR_B200_ATTN_SPLIT")) split = atoi(e);  // tuning override (0: never split)
+  rt_status s = build_attn_plan(*cfg, lens, n_seq, kv_ptr, kv_idx, visits, n_ctas, p->host, split);
   if (s != RT_OK) {
     delete p;
     return s;
@@ -646,7 +723,10 @@ extern "C" rt_status rt_attn_plan_create(const rt_config* cfg, const int32_t* le
   p->items_off = 0;
   p->entries_off = align(p->host.items.size() * sizeof(AttnItem));
   p->cta_off = p->entries_off + align(p->host.entries.size() * sizeof(int32_t));
-  p->bytes = p->cta_off + align(p->host.cta_ptr.size() * sizeof(int32_t));
+  p->groups_off = p->cta_off + align(p->host.cta_ptr.size() * sizeof(int32_t));
+  p->part_o_off = p->groups_off + align(p->host.groups.size() * sizeof(int32_t));
+  p->part_ml_off = p->part_o_off + align(static_cast<size_t>(p->host.n_slots) * 128 * 64 * sizeof(float));
+  p->bytes = p->part_ml_off + align(static_cast<size_t>(p->host.n_slots) * 128 * 2 * sizeof(float)) + 256;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t e = cudaMalloc(&p->dev, p->bytes);
   if (e == cudaSuccess)
@@ -657,6 +737,9 @@ extern "C" rt_status rt_attn_plan_create(const rt_config* cfg, const int32_t* le
                         cudaMemcpyHostToDevice, st);
   if (e == cudaSuccess)
     e = cudaMemcpyAsync(p->dev + p->cta_off, p->host.cta_ptr.data(), p->host.cta_ptr.size() * sizeof(int32_t),
+                        cudaMemcpyHostToDevice, st);
+  if (e == cudaSuccess && !p->host.groups.empty())
+    e = cudaMemcpyAsync(p->dev + p->groups_off, p->host.groups.data(), p->host.groups.size() * sizeof(int32_t),
                         cudaMemcpyHostToDevice, st);
   if (e == cudaSuccess) e = cudaStreamSynchronize(st);
   if (e != cudaSuccess) {
@@ -691,7 +774,11 @@ extern "C" rt_status rt_sparse_attention(void* ctx, const void* q, const void* k
                                  reinterpret_cast<const int32_t*>(plan->dev + plan->entries_off),
                                  reinterpret_cast<const int32_t*>(plan->dev + plan->cta_off), plan->n_ctas,
                                  plan->host.total_tokens, plan->host.heads, scale, dtype,
-                                 static_cast<cudaStream_t>(stream));
+                                 static_cast<cudaStream_t>(stream), nullptr,
+                                 AttnSplit{reinterpret_cast<const int32_t*>(plan->dev + plan->groups_off),
+                                           static_cast<int>(plan->host.groups.size() / 6),
+                                           reinterpret_cast<float*>(plan->dev + plan->part_o_off),
+                                           reinterpret_cast<float*>(plan->dev + plan->part_ml_off)});
 }
 
 #ifdef RT_ATTN_TRACE

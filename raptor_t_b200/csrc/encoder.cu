@@ -150,7 +150,9 @@ struct rt_encoder {
   } slots[2];
   uint64_t batch_counter = 0;
   Slot* cur = nullptr;
-  size_t region_bytes = 0, items_off = 0, entries_off = 0, cta_off = 0;
+  size_t region_bytes = 0, items_off = 0, entries_off = 0, cta_off = 0, groups_off = 0;
+  std::vector<int> plan_groups;        // per layer: split lists to merge
+  DevBuf part_o, part_ml;              // partial results of split lists (shared by all layers)
   std::vector<BlockCsr> csr;           // per layer, host copy (tests / accessors)
   std::vector<int64_t> plan_entries;   // per layer
   int64_t plan_visits = 0;
@@ -259,21 +261,26 @@ void worker_main(rt_encoder* e) {
       const size_t items_b = plan.items.size() * sizeof(AttnItem);
       const size_t entries_b = plan.entries.size() * sizeof(int32_t);
       const size_t cta_b = plan.cta_ptr.size() * sizeof(int32_t);
+      const size_t groups_b = plan.groups.size() * sizeof(int32_t);
       if (e->items_off + items_b > e->entries_off || e->entries_off + entries_b > e->cta_off ||
-          e->cta_off + cta_b > e->region_bytes) {
+          e->cta_off + cta_b > e->groups_off || e->groups_off + groups_b > e->region_bytes ||
+          static_cast<size_t>(plan.n_slots) * 128 * 64 * sizeof(float) > e->part_o.bytes) {
         s = RT_ERR_STATE;
         last_error_ref() = "metadata region overflow";
       } else {
         std::memcpy(host + e->items_off, plan.items.data(), items_b);
         std::memcpy(host + e->entries_off, plan.entries.data(), entries_b);
         std::memcpy(host + e->cta_off, plan.cta_ptr.data(), cta_b);
+        std::memcpy(host + e->groups_off, plan.groups.data(), groups_b);
+        e->plan_groups[l] = static_cast<int>(plan.groups.size() / 6);
         cudaError_t ce = cudaMemcpyAsync(dev + e->items_off, host + e->items_off, items_b, cudaMemcpyHostToDevice,
                                          e->meta_stream);
         if (ce == cudaSuccess)
           ce = cudaMemcpyAsync(dev + e->entries_off, host + e->entries_off, entries_b, cudaMemcpyHostToDevice,
                                e->meta_stream);
         if (ce == cudaSuccess)
-          ce = cudaMemcpyAsync(dev + e->cta_off, host + e->cta_off, cta_b, cudaMemcpyHostToDevice, e->meta_stream);
+          ce = cudaMemcpyAsync(dev + e->cta_off, host + e->cta_off, cta_b + (e->groups_off - e->cta_off - cta_b) + groups_b,
+                               cudaMemcpyHostToDevice, e->meta_stream);  // per-CTA offsets and the groups behind them
         if (ce == cudaSuccess) ce = cudaEventRecord(slot.table_ready[l], e->meta_stream);
         if (ce != cudaSuccess) {
           s = RT_ERR_CUDA;
@@ -362,7 +369,9 @@ rt_status run_attention(rt_encoder* e, int l, const void* input, void* output, c
     RT_TRY(launch_sparse_attention(ctx, q, k, v, reinterpret_cast<const AttnItem*>(dev + e->items_off),
                                    reinterpret_cast<const int32_t*>(dev + e->entries_off),
                                    reinterpret_cast<const int32_t*>(dev + e->cta_off), e->attn_ctas, T, c.heads, 1.0f, dt,
-                                   st));
+                                   st, nullptr,
+                                   AttnSplit{reinterpret_cast<const int32_t*>(dev + e->groups_off), e->plan_groups[l],
+                                             static_cast<float*>(e->part_o.p), static_cast<float*>(e->part_ml.p)}));
   }
   if (e->fuse_residual) {
     {
@@ -444,6 +453,7 @@ extern "C" rt_status rt_encoder_create(const rt_config* cfg, rt_encoder** out) {
   e->csr.resize(cfg->layers);
   e->csr_valid.assign(cfg->layers, false);
   e->plan_entries.assign(cfg->layers, 0);
+  e->plan_groups.assign(cfg->layers, 0);
   cudaGetDevice(&e->device);
   cudaDeviceGetAttribute(&e->sm_count, cudaDevAttrMultiProcessorCount, e->device);
   e->attn_ctas = 2 * e->sm_count;
@@ -469,7 +479,8 @@ extern "C" rt_status rt_encoder_destroy(rt_encoder* e) {
     for (DevBuf* b : {&l.qkv_w, &l.qkv_b, &l.ao_w, &l.ao_b, &l.aln_g, &l.aln_b, &l.up_w, &l.up_b, &l.down_w, &l.down_b,
                       &l.oln_g, &l.oln_b})
       b->release();
-  for (DevBuf* b : {&e->emb_word, &e->emb_pos, &e->emb_type, &e->emb_g, &e->emb_b, &e->ids_dev, &e->pos_dev})
+  for (DevBuf* b : {&e->emb_word, &e->emb_pos, &e->emb_type, &e->emb_g, &e->emb_b, &e->ids_dev, &e->pos_dev, &e->part_o,
+                    &e->part_ml})
     b->release();
   for (auto& kv : e->scratch) kv.second.release();
   for (auto& slot : e->slots) {
@@ -601,11 +612,23 @@ extern "C" rt_status rt_encoder_prepare_batch(rt_encoder* e, const int32_t* lens
   // per-layer regions
   int64_t visits = 0;
   RT_TRY(rt_count_visits(&e->cfg, lens, n_seq, &visits));
-  const size_t n_items = static_cast<size_t>(count_items_per_head(e->cfg, e->lens)) * e->cfg.heads;
+  // split lists: at most one group per (sequence, head); every part is one more item and one scratch slot
+  size_t slots_bound = 0;
+  for (int q = 0; q < n_seq; ++q)
+    slots_bound += static_cast<size_t>(lens[q] / e->cfg.block + kDefaultSplitEntries - 1) / kDefaultSplitEntries + 1;
+  slots_bound *= e->cfg.heads;
+  const size_t groups_bound = static_cast<size_t>(n_seq) * e->cfg.heads;
+  const size_t n_items = static_cast<size_t>(count_items_per_head(e->cfg, e->lens)) * e->cfg.heads + slots_bound;
   e->items_off = 0;
   e->entries_off = align256(n_items * sizeof(AttnItem));
   e->cta_off = e->entries_off + align256(static_cast<size_t>(visits) * e->cfg.heads * sizeof(int32_t));
-  e->region_bytes = e->cta_off + align256((e->attn_ctas + 1) * sizeof(int32_t));
+  e->groups_off = e->cta_off + align256((e->attn_ctas + 1) * sizeof(int32_t));
+  e->region_bytes = e->groups_off + align256(groups_bound * 6 * sizeof(int32_t));
+  if (slots_bound * 128 * 64 * sizeof(float) > e->part_o.bytes) {
+    RT_CHECK_CUDA(cudaDeviceSynchronize());
+    RT_TRY(e->part_o.ensure(slots_bound * 128 * 64 * sizeof(float)));
+    RT_TRY(e->part_ml.ensure(slots_bound * 128 * 2 * sizeof(float)));
+  }
   const size_t need = e->region_bytes * e->cfg.layers;
   if (need > slot.meta_cap) {
     if (slot.meta_pinned) cudaFreeHost(slot.meta_pinned);

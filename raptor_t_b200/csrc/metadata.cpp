@@ -348,6 +348,38 @@ struct ItemRef {
   AttnItem it;
 };
 
+// Cuts lists longer than `split` entries into near-equal parts; each part becomes an item of
+// its own that writes a partial result to a scratch slot.
+void split_long_items(std::vector<ItemRef>& refs, int split, AttnPlanHost& out) {
+  out.groups.clear();
+  out.n_slots = 0;
+  if (split <= 0) return;
+  std::vector<ItemRef> res;
+  res.reserve(refs.size());
+  for (const ItemRef& r : refs) {
+    if (r.n_entries <= split) {
+      res.push_back(r);
+      continue;
+    }
+    const int parts = (r.n_entries + split - 1) / split;
+    const int base = r.n_entries / parts, extra = r.n_entries % parts;
+    const int32_t g[6] = {out.n_slots, parts, r.it.out_tok0, r.it.out_tok1, r.it.head, 0};
+    out.groups.insert(out.groups.end(), g, g + 6);
+    int off = 0;
+    for (int p = 0; p < parts; ++p) {
+      ItemRef part = r;
+      part.n_entries = base + (p < extra ? 1 : 0);
+      part.ent = r.ent + off;
+      part.it.n_entries = part.n_entries;
+      part.it.head = r.it.head | ((out.n_slots + 1) << 8);
+      off += part.n_entries;
+      ++out.n_slots;
+      res.push_back(part);
+    }
+  }
+  refs.swap(res);
+}
+
 void assign_and_emit(std::vector<ItemRef>& refs, int n_ctas, AttnPlanHost& out) {
   // longest-processing-time assignment of items to CTAs (+2: per-item prologue/epilogue cost)
   std::vector<int> order(refs.size());
@@ -391,7 +423,8 @@ void assign_and_emit(std::vector<ItemRef>& refs, int n_ctas, AttnPlanHost& out) 
 }  // namespace
 
 rt_status build_attn_plan(const rt_config& cfg, const int32_t* lens, int n_seq, const int32_t* kv_ptr,
-                          const int32_t* kv_idx, int64_t visits_per_head, int n_ctas, AttnPlanHost& out) {
+                          const int32_t* kv_idx, int64_t visits_per_head, int n_ctas, AttnPlanHost& out,
+                          int split_entries) {
   RT_REQUIRE(n_ctas > 0, RT_ERR_INVALID, "attention plan needs at least one CTA");
   const int nh = cfg.heads, B = cfg.block;
   std::vector<int32_t> pool;  // all merged lists, back to back
@@ -438,6 +471,7 @@ rt_status build_attn_plan(const rt_config& cfg, const int32_t* lens, int n_seq, 
   }
   std::vector<ItemRef> refs(pend.size());
   for (size_t i = 0; i < pend.size(); ++i) refs[i] = ItemRef{pend[i].n, pool.data() + pend[i].off, pend[i].it};
+  split_long_items(refs, split_entries, out);
   assign_and_emit(refs, n_ctas, out);
   out.total_tokens = tok0;
   out.heads = nh;
@@ -489,7 +523,8 @@ rt_status build_seq_template(const rt_config& cfg, uint32_t seed, int L, TableCa
 }
 
 rt_status assemble_attn_plan(const rt_config& cfg, const int32_t* lens, int n_seq,
-                             const SeqTemplate* const* templates, int n_ctas, AttnPlanHost& out) {
+                             const SeqTemplate* const* templates, int n_ctas, AttnPlanHost& out,
+                             int split_entries) {
   RT_REQUIRE(n_ctas > 0, RT_ERR_INVALID, "attention plan needs at least one CTA");
   const int nh = cfg.heads, B = cfg.block;
   out = AttnPlanHost();
@@ -522,6 +557,7 @@ rt_status assemble_attn_plan(const rt_config& cfg, const int32_t* lens, int n_se
     out.visits += t.visits;
     tok0 += lens[s];
   }
+  split_long_items(refs, split_entries, out);
   assign_and_emit(refs, n_ctas, out);
   out.total_tokens = tok0;
   out.heads = nh;

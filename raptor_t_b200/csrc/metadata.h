@@ -67,20 +67,29 @@ struct AttnItem {
   int32_t n_entries;
   int32_t out_tok0;   // first token (packed) of query block A
   int32_t out_tok1;   // first token of query block B, or -1
-  int32_t head;
+  int32_t head;       // bits 0-7: head; bits 8-31: 1 + partial-result slot when the item is one part of a split list
 };
 
 struct AttnPlanHost {
   std::vector<AttnItem> items;     // ordered by CTA
   std::vector<int32_t> entries;    // (local block id << 2) | mask; mask bit0: block A uses it, bit1: block B
   std::vector<int32_t> cta_ptr;    // [n_ctas+1]
+  // Long lists (the global query blocks attend to every block) are cut into parts of at most
+  // `split` entries; every part is a work item that leaves an un-normalised partial result
+  // (fp32 output tile + row max + row sum) in scratch slot, and a merge kernel combines the
+  // parts of a group.  groups: 6 int32 each {first_slot, n_parts, out_tok0, out_tok1, head, 0}.
+  std::vector<int32_t> groups;
+  int n_slots = 0;
   int64_t visits = 0;              // useful (query block, key block) pairs, all heads
   int total_tokens = 0;
   int heads = 0;
 };
 
+// split_entries: lists longer than this are cut into parts (0 = never split).
+constexpr int kDefaultSplitEntries = 24;
 rt_status build_attn_plan(const rt_config& cfg, const int32_t* lens_tokens, int n_seq, const int32_t* kv_ptr,
-                          const int32_t* kv_idx, int64_t visits_per_head, int n_ctas, AttnPlanHost& out);
+                          const int32_t* kv_idx, int64_t visits_per_head, int n_ctas, AttnPlanHost& out,
+                          int split_entries = kDefaultSplitEntries);
 
 // Work-list template of ONE sequence of n_blocks blocks under one table seed, all heads:
 // the query-block pairs and their merged, masked key/value lists with sequence-local
@@ -101,6 +110,7 @@ rt_status build_seq_template(const rt_config& cfg, uint32_t seed, int n_blocks, 
 // Assemble the batch work list from per-sequence templates (templates[s] for sequence s)
 // and assign items to CTAs (longest processing time first).
 rt_status assemble_attn_plan(const rt_config& cfg, const int32_t* lens_tokens, int n_seq,
-                             const SeqTemplate* const* templates, int n_ctas, AttnPlanHost& out);
+                             const SeqTemplate* const* templates, int n_ctas, AttnPlanHost& out,
+                             int split_entries = kDefaultSplitEntries);
 
 }  // namespace rt

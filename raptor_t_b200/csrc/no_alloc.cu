@@ -106,7 +106,8 @@ extern "C" rt_status rt_sparse_attention_static(void* ctx_dev, const void* q_dev
   int n_blocks = 0;
   for (int s = 0; s < n_seq; ++s) n_blocks += lens_tokens_host[s] / cfg->block;
   AttnPlanHost plan;  // host memory only
-  RT_TRY(build_attn_plan(*cfg, lens_tokens_host, n_seq, kv_ptr_host, kv_idx_host, kv_ptr_host[n_blocks], n_ctas, plan));
+  RT_TRY(build_attn_plan(*cfg, lens_tokens_host, n_seq, kv_ptr_host, kv_idx_host, kv_ptr_host[n_blocks], n_ctas, plan,
+                         /*split_entries=*/0));  // partial results would need more scratch: lists stay whole
   RT_REQUIRE(static_cast<int>(plan.items.size()) <= kMaxItems && static_cast<int>(plan.entries.size()) <= kMaxEntries,
              RT_ERR_UNSUPPORTED,
              "sparse_attention_static: batch needs %zu work items / %zu list entries, the static scratch holds %d / %d "

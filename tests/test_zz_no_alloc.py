@@ -30,9 +30,13 @@ def _case(cfg, lens, layer, seed, dtype):
     return ref, out, free_before - free_after
 
 
-def test_static_scratch_entry_matches_regular_entry_twice_in_a_row():
+def test_static_scratch_entry_matches_regular_entry_twice_in_a_row(monkeypatch):
     if not torch.cuda.is_available():
         pytest.skip("needs a CUDA device")
+    # the regular entry point cuts long lists into parts merged by a second kernel (another
+    # summation order); the static one keeps lists whole.  With splitting off both run the
+    # same work list, so the comparison can be exact.
+    monkeypatch.setenv("RAPTOR_B200_ATTN_SPLIT", "0")
     from raptor_t_b200 import capi
     cfg = capi.make_config(hidden=768, heads=12, ffn=3072, layers=1, dtype="bf16")
     # first call: a larger batch; second call: a smaller, different one (stale work-list
