@@ -230,6 +230,17 @@ rt_status rt_encoder_forward_ids(rt_encoder* enc, const int32_t* ids_dev, const 
  * D2H of the final hidden states; returns after the output is in out_host. */
 rt_status rt_encoder_forward_host(rt_encoder* enc, const int32_t* lens_tokens, int n_seq,
                                   const int32_t* ids_host, void* out_host);
+/* The same in two halves, so that a caller keeps two batches in flight: submit enqueues
+ * prepare_batch + H2D + forward on the encoder's own stream and the D2H of the result on a
+ * second stream (the copy of batch i overlaps the kernels of batch i+1) and returns at once
+ * with a ticket; wait blocks until that batch's output is in out_host.  ids_host and out_host
+ * belong to the library between the two calls (pinned memory, or the copies block).  A third
+ * submit first waits for the oldest batch.  rt_encoder_forward_host == submit + wait.
+ * For drivers shaped like the batch loop of python/benchmark/end2end.py:79-89 (one
+ * update_meta_data + one model call per batch) that feed from and return to host memory. */
+rt_status rt_encoder_submit_host(rt_encoder* enc, const int32_t* lens_tokens, int n_seq, const int32_t* ids_host,
+                                 void* out_host, uint64_t* ticket);
+rt_status rt_encoder_wait_host(rt_encoder* enc, uint64_t ticket);
 
 /* The three operators of python/pybind.cpp:12-56 on one layer's weights.
  * attention: layers/multi_headed_attention.cpp:154-216; intermediate: layers/bert_intermediate.cpp:7-29;

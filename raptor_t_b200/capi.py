@@ -77,6 +77,8 @@ _SIGS = {
     "rt_encoder_forward_hidden": (C.c_int, [_vp, _vp, C.c_int, C.c_int, _vp]),
     "rt_encoder_forward_ids": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp]),
     "rt_encoder_forward_host": (C.c_int, [_vp, _i32p, C.c_int, _vp, _vp]),
+    "rt_encoder_submit_host": (C.c_int, [_vp, _i32p, C.c_int, _vp, _vp, C.POINTER(C.c_uint64)]),
+    "rt_encoder_wait_host": (C.c_int, [_vp, C.c_uint64]),
     "rt_encoder_attention": (C.c_int, [_vp, C.c_int, _vp, _vp, _vp]),
     "rt_encoder_intermediate": (C.c_int, [_vp, C.c_int, _vp, _vp, _vp]),
     "rt_encoder_output": (C.c_int, [_vp, C.c_int, _vp, _vp, _vp, _vp]),

@@ -54,7 +54,11 @@ using namespace ptx;
 constexpr int kThreads = 192;
 constexpr int kStagesK = 4;              // K ring depth (a slot is free again once the S MMA has read it)
 constexpr int kStagesV = 5;              // V ring depth (a slot is held until the PV MMA, two softmax periods later)
-constexpr int kMaskRing = 16;            // entry masks travel from the producer to the softmax warps through smem
+constexpr int kEntRing = 32;             // per-entry records travel from the K cursor to the other roles through smem
+constexpr int kEntStage = 16;            // landing slots of the asynchronous work-list reads
+constexpr int kEntAhead = 8;             // how many list entries the producer reads ahead
+constexpr int kEntFirst = 1 << 29;       // record flags: first / last entry of its item
+constexpr int kEntLast = 1 << 30;
 constexpr int kTileBytes = 64 * 64 * 2;  // one 64 x 64 16-bit block
 constexpr int kQBytes = 2 * kTileBytes;
 constexpr int kTmemCols = 256;
@@ -70,11 +74,36 @@ struct Smem {
   uint64_t q_full[2], q_empty[2];
   uint64_t k_full[kStagesK], k_empty[kStagesK], v_full[kStagesV], v_empty[kStagesV];
   uint64_t s_full[2], s_free[2], p_full[2], pv_done[2], o_free;
-  int32_t mask_ring[kMaskRing];
+  int2 ent_ring[kEntRing];      // {entry (block << 2 | mask) | flags, row of the key/value block}
+  int32_t ent_stage[kEntStage];
   uint32_t tmem_slot;
   int abort_flag;
 };
 constexpr int kSmemBytes = sizeof(Smem);
+
+// 4-byte asynchronous global -> shared copies: the producer thread reads its work list
+// ahead without ever stalling on a global load.
+__device__ __forceinline__ void cp_async_4(void* dst_smem, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// A CTA's items are consecutive and so are their lists: [first, first + count) of `entries`.
+__device__ __forceinline__ void cta_entry_range(const AttnItem* items, int item_begin, int item_end, int& first,
+                                                uint32_t& count) {
+  first = 0;
+  count = 0;
+  if (item_begin < item_end) {
+    const int a = items[item_begin].entry_off;
+    const AttnItem& z = items[item_end - 1];
+    first = a;
+    count = static_cast<uint32_t>(z.entry_off + z.n_entries - a);
+  }
+}
 
 __device__ __forceinline__ float ex2(float x) {
   float y;
@@ -214,42 +243,49 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 
   if (warp == 4) {
     // ------------------------------------------------------------------ TMA producer
-    // One thread feeds two rings from the same flattened (item, entry) stream with two
-    // cursors: the K cursor (which also loads each item's Q tile and publishes the entry
-    // masks) may run ahead of the V cursor, because K slots are recycled earlier.
+    // One thread walks the CTA's flattened (item, entry) stream with three cursors: K loads
+    // (which also load each item's Q tile and publish one record per entry), V loads and the
+    // S = Q K^T issue.  Only the K cursor touches the work list in global memory: the entries
+    // arrive through asynchronous copies issued kEntAhead entries early and the next item is
+    // prefetched in registers, so no cursor ever waits on a global load.  The V and S cursors
+    // (and the PV and softmax warps) take what they need from the records in shared memory.
     if (lane == 0) {
       prefetch_tensormap(&map_q);
       prefetch_tensormap(&map_k);
       prefetch_tensormap(&map_v);
       constexpr uint32_t idesc_s = make_idesc_f16(128, 64, BF16 ? 1 : 0, false);
-      int k_item = item_begin, k_j = 0, v_item = item_begin, v_j = 0;
-      uint32_t k_g = 0, v_g = 0, k_itn = 0;
-      AttnItem ki{}, vi{};
-      int s_item = item_begin, s_j = 0, s_n = 0;  // S = Q K^T issue cursor (behind the K cursor)
-      uint32_t s_g = 0, s_itn = 0;
-      auto next_s_item = [&]() {
-        while (s_item < item_end && (s_n = items[s_item].n_entries) == 0) ++s_item;
+      int ent_first;
+      uint32_t total;
+      cta_entry_range(items, item_begin, item_end, ent_first, total);
+      const int32_t* ent = entries + ent_first;
+      auto fetch = [&](uint32_t i) {
+        if (i < total) cp_async_4(&sm.ent_stage[i % kEntStage], ent + i);
+        cp_async_commit();  // one group per entry, empty past the end: the wait below counts groups
       };
-      next_s_item();
-      auto load_item = [&](int& item, AttnItem& dst) {
-        while (item < item_end) {
-          dst = items[item];
-          if (dst.n_entries > 0) break;
-          ++item;
+      for (uint32_t i = 0; i < kEntAhead; ++i) fetch(i);
+      int k_item = item_begin, k_j = 0;
+      uint32_t k_g = 0, v_g = 0, s_g = 0, k_itn = 0, s_itn = 0;
+      AttnItem ki{}, kn{};
+      auto settle_item = [&]() {  // k_item -> first item with a non-empty list; prefetch the one after it
+        while (k_item < item_end && ki.n_entries == 0) {
+          ++k_item;
+          if (k_item < item_end) ki = items[k_item];
         }
+        if (k_item + 1 < item_end) kn = items[k_item + 1];
       };
-      load_item(k_item, ki);
-      load_item(v_item, vi);
+      if (k_item < item_end) ki = items[k_item];
+      settle_item();
       bool q_loaded = false;
       long long idle_since = clock64();
       volatile int* abort_flag = &sm.abort_flag;
-      while ((k_item < item_end || v_item < item_end || s_item < item_end) && !*abort_flag) {
+      while ((k_g < total || v_g < total || s_g < total) && !*abort_flag) {
         bool progress = false;
-        if (s_item < item_end && s_g < k_g) {
+        if (s_g < k_g) {
+          const int rec = sm.ent_ring[s_g % kEntRing].x;
           const int qb = s_itn & 1;
           const int b = s_g & 1;
           const int st = s_g % kStagesK;
-          if ((s_j > 0 || mbar_test_wait(&sm.q_full[qb], (s_itn >> 1) & 1)) &&
+          if ((!(rec & kEntFirst) || mbar_test_wait(&sm.q_full[qb], (s_itn >> 1) & 1)) &&
               mbar_test_wait(&sm.k_full[st], (s_g / kStagesK) & 1) &&
               mbar_test_wait(&sm.s_free[b], ((s_g >> 1) & 1) ^ 1)) {
             tc_fence_after_sync();
@@ -262,17 +298,14 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             tc_commit(&sm.s_full[b]);
             TRACE(5, s_g)
             ++s_g;
-            if (++s_j == s_n) {
+            if (rec & kEntLast) {
               tc_commit(&sm.q_empty[qb]);
               ++s_itn;
-              ++s_item;
-              s_j = 0;
-              next_s_item();
             }
             progress = true;
           }
         }
-        if (k_item < item_end) {
+        if (k_g < total) {
           const int qb = k_itn & 1;
           if (!q_loaded && mbar_test_wait(&sm.q_empty[qb], ((k_itn >> 1) & 1) ^ 1)) {
             mbar_arrive_expect_tx(&sm.q_full[qb], kQBytes);
@@ -283,48 +316,50 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           }
           const int s = k_g % kStagesK;
           if (q_loaded && mbar_test_wait(&sm.k_empty[s], ((k_g / kStagesK) & 1) ^ 1)) {
-            const int e = entries[ki.entry_off + k_j];
-            sm.mask_ring[k_g % kMaskRing] = e & 3;
+            cp_async_wait<kEntAhead - 1>();  // the copy of entry k_g has landed
+            const int e = *reinterpret_cast<volatile int32_t*>(&sm.ent_stage[k_g % kEntStage]);
+            fetch(k_g + kEntAhead);
+            const int row = ki.kv_row0 + (e >> 2) * 64;
+            const bool last = k_j + 1 == ki.n_entries;
+            sm.ent_ring[k_g % kEntRing] = make_int2(e | (k_j == 0 ? kEntFirst : 0) | (last ? kEntLast : 0), row);
             mbar_arrive_expect_tx(&sm.k_full[s], kTileBytes);
-            tma_load_2d(sm.k[s], &map_k, 0, ki.kv_row0 + (e >> 2) * 64, &sm.k_full[s]);
+            tma_load_2d(sm.k[s], &map_k, 0, row, &sm.k_full[s]);
             TRACE(1, k_g)
             ++k_g;
-            if (++k_j == ki.n_entries) {
+            ++k_j;
+            if (last) {
               ++k_item;
               ++k_itn;
               k_j = 0;
               q_loaded = false;
-              load_item(k_item, ki);
+              ki = kn;
+              settle_item();
             }
             progress = true;
           }
         }
-        if (v_item < item_end && v_g < k_g) {
+        if (v_g < k_g) {
           const int s = v_g % kStagesV;
           if (mbar_test_wait(&sm.v_empty[s], ((v_g / kStagesV) & 1) ^ 1)) {
-            const int e = entries[vi.entry_off + v_j];
+            const int row = sm.ent_ring[v_g % kEntRing].y;
             mbar_arrive_expect_tx(&sm.v_full[s], kTileBytes);
-            tma_load_2d(sm.v[s], &map_v, 0, vi.kv_row0 + (e >> 2) * 64, &sm.v_full[s]);
+            tma_load_2d(sm.v[s], &map_v, 0, row, &sm.v_full[s]);
             TRACE(2, v_g)
             ++v_g;
-            if (++v_j == vi.n_entries) {
-              ++v_item;
-              v_j = 0;
-              load_item(v_item, vi);
-            }
             progress = true;
           }
         }
         if (progress) {
           idle_since = clock64();
         } else {
-          __nanosleep(250);  // nothing to do yet (all jobs run entries ahead): leave the issue slots to the softmax warps
+          __nanosleep(64);  // nothing to do yet (all cursors run ahead): leave the issue slots to the softmax warps
           if (clock64() - idle_since > kWaitCycles) {
             *abort_flag = 1;
             atomicCAS(error_flag, 0, 201);
           }
         }
       }
+      cp_async_wait<0>();
       // Leaving on an abort happens only after the pipeline has been idle for the whole
       // time-out, so none of this thread's copies can still be in flight.
     }
@@ -334,48 +369,39 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       constexpr uint32_t idesc_pv = make_idesc_f16(128, 64, BF16 ? 1 : 0, true);
       // this thread issues the PV MMAs; the S MMAs are issued by the producer thread, so the
       // two serial issue chains (waits, four MMAs, commits per entry) run side by side
-      int pv_item = item_begin, pv_j = 0, pv_n = 0;
-      uint32_t pv_g = 0;
-      bool ok = true;
-      auto skip_empty = [&](int& item, int& n) {
-        while (item < item_end && (n = items[item].n_entries) == 0) ++item;
-      };
-      skip_empty(pv_item, pv_n);
+      int ent_first;
+      uint32_t total;
+      cta_entry_range(items, item_begin, item_end, ent_first, total);
       uint32_t pv_itn = 0;
-      auto issue_pv = [&]() -> bool {
+      bool ok = true;
+      for (uint32_t pv_g = 0; ok && pv_g < total; ++pv_g) {
         const int b = pv_g & 1;
         const uint32_t u = pv_g >> 1;
         const int st = pv_g % kStagesV;
         const uint32_t ph = (pv_g / kStagesV) & 1;
         TRACE(6, pv_g)
-        if (!mbar_wait(&sm.v_full[st], ph, ab, 214)) return false;
+        if (!mbar_wait(&sm.v_full[st], ph, ab, 214)) { ok = false; break; }
         TRACE(7, pv_g)
-        if (pv_j == 0) {
+        // the producer wrote this entry's record before it issued the V copy just waited for
+        const int rec = *reinterpret_cast<volatile int*>(&sm.ent_ring[pv_g % kEntRing].x);
+        const bool first = (rec & kEntFirst) != 0;
+        if (first) {
           // the output tile is overwritten: the softmax warps must have read the previous item's result
-          if (!mbar_wait(&sm.o_free, (pv_itn & 1) ^ 1, ab, 215)) return false;
+          if (!mbar_wait(&sm.o_free, (pv_itn & 1) ^ 1, ab, 215)) { ok = false; break; }
         }
-        if (!mbar_wait(&sm.p_full[b], u & 1, ab, 216)) return false;
+        if (!mbar_wait(&sm.p_full[b], u & 1, ab, 216)) { ok = false; break; }
         TRACE(8, pv_g)
         tc_fence_after_sync();
         const uint64_t dv = make_smem_desc_sw128(smem_u32(sm.v[st]));
         const uint32_t d = tmem_base + kColO;
         const uint32_t a = tmem_base + kColP + b * 32;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) mma_ts(d, a + k * 8, dv + (k * 2048 >> 4), idesc_pv, (pv_j | k) ? 1u : 0u);
+        for (int k = 0; k < 4; ++k) mma_ts(d, a + k * 8, dv + (k * 2048 >> 4), idesc_pv, (!first || k) ? 1u : 0u);
         tc_commit(&sm.v_empty[st]);
         tc_commit(&sm.pv_done[b]);
         TRACE(9, pv_g)
-        ++pv_g;
-        if (++pv_j == pv_n) {
-          ++pv_item;
-          ++pv_itn;
-          pv_j = 0;
-          skip_empty(pv_item, pv_n);
-        }
-        return true;
-      };
-
-      while (ok && pv_item < item_end) ok = issue_pv();
+        if (rec & kEntLast) ++pv_itn;
+      }
     }
   } else {
     // ------------------------------------------------------------------ softmax warps 0..3
@@ -403,8 +429,8 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         TRACE(11, gj)
         PROF_MARK(1)
         tc_fence_after_sync();
-        // the producer published this entry's mask before it loaded the K block of the S tile just waited for
-        const bool active = ((sm.mask_ring[gj % kMaskRing] >> half) & 1) != 0;
+        // the producer published this entry's record before it loaded the K block of the S tile just waited for
+        const bool active = ((sm.ent_ring[gj % kEntRing].x >> half) & 1) != 0;
         uint32_t s[64];
         if (active) {
           tmem_ld32(lane_base + kColS + b * 64, s);

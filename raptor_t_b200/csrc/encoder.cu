@@ -162,6 +162,19 @@ struct rt_encoder {
   std::vector<bool> csr_valid;         // host CSR copies are built on demand
 
   cudaStream_t meta_stream = nullptr;
+
+  // Host-buffer pipeline (rt_encoder_submit_host / rt_encoder_wait_host): batches run back
+  // to back on pipe_stream, each into its own device output buffer, and copy_stream carries
+  // a finished batch to the caller's memory while the next batch computes.
+  struct HostJob {
+    DevBuf out;
+    cudaEvent_t computed = nullptr, copied = nullptr;
+    int* err_host = nullptr;  // pinned copy of the device error word, taken behind the output copy
+    bool busy = false;
+    uint64_t ticket = 0;
+  } jobs[2];
+  cudaStream_t pipe_stream = nullptr, copy_stream = nullptr;
+  uint64_t next_ticket = 1;
   std::thread worker;
   std::mutex mu;
   std::condition_variable cv;
@@ -493,6 +506,14 @@ extern "C" rt_status rt_encoder_destroy(rt_encoder* e) {
     for (auto& ev : slot.table_ready) cudaEventDestroy(ev);
   }
   for (auto& ev : e->timer.pool) cudaEventDestroy(ev);
+  for (auto& job : e->jobs) {
+    job.out.release();
+    if (job.computed) cudaEventDestroy(job.computed);
+    if (job.copied) cudaEventDestroy(job.copied);
+    if (job.err_host) cudaFreeHost(job.err_host);
+  }
+  if (e->pipe_stream) cudaStreamDestroy(e->pipe_stream);
+  if (e->copy_stream) cudaStreamDestroy(e->copy_stream);
   if (e->meta_stream) cudaStreamDestroy(e->meta_stream);
   delete e;
   return RT_OK;
@@ -733,21 +754,67 @@ extern "C" rt_status rt_encoder_forward_ids(rt_encoder* e, const int32_t* ids, c
   return end_forward(e, st);
 }
 
-extern "C" rt_status rt_encoder_forward_host(rt_encoder* e, const int32_t* lens, int n_seq, const int32_t* ids_host,
-                                             void* out_host) {
-  RT_REQUIRE(e && ids_host && out_host, RT_ERR_INVALID, "forward_host: null pointer");
+extern "C" rt_status rt_encoder_submit_host(rt_encoder* e, const int32_t* lens, int n_seq, const int32_t* ids_host,
+                                            void* out_host, uint64_t* ticket) {
+  RT_REQUIRE(e && ids_host && out_host && ticket, RT_ERR_INVALID, "submit_host: null pointer");
+  if (!e->pipe_stream) {
+    RT_CHECK_CUDA(cudaStreamCreateWithFlags(&e->pipe_stream, cudaStreamNonBlocking));
+    RT_CHECK_CUDA(cudaStreamCreateWithFlags(&e->copy_stream, cudaStreamNonBlocking));
+    for (auto& job : e->jobs) {
+      RT_CHECK_CUDA(cudaEventCreateWithFlags(&job.computed, cudaEventDisableTiming));
+      RT_CHECK_CUDA(cudaEventCreateWithFlags(&job.copied, cudaEventDisableTiming));
+      RT_CHECK_CUDA(cudaMallocHost(&job.err_host, sizeof(int)));
+      *job.err_host = 0;
+    }
+  }
+  rt_encoder::HostJob& job = e->jobs[e->next_ticket & 1];
+  if (job.busy) {  // at most two batches in flight: this buffer's previous batch must have reached the host
+    RT_CHECK_CUDA(cudaEventSynchronize(job.copied));
+    job.busy = false;
+  }
+  // a forward issued through the device-buffer entry points on another stream shares the scratch
+  rt_encoder::Slot* prev = e->cur;
   RT_TRY(rt_encoder_prepare_batch(e, lens, n_seq));
+  if (prev && prev->forward_recorded) RT_CHECK_CUDA(cudaStreamWaitEvent(e->pipe_stream, prev->forward_done, 0));
   const size_t T = e->tokens;
   RT_TRY(e->ids_dev.ensure(T * sizeof(int32_t)));
   const size_t out_bytes = T * e->cfg.hidden * 2;
-  RT_TRY(e->scratch["host_out"].ensure(out_bytes));
-  cudaStream_t st = nullptr;
+  RT_TRY(job.out.ensure(out_bytes));
+  cudaStream_t st = e->pipe_stream;
   RT_CHECK_CUDA(cudaMemcpyAsync(e->ids_dev.p, ids_host, T * sizeof(int32_t), cudaMemcpyHostToDevice, st));
-  void* out_dev = e->scratch["host_out"].p;
-  RT_TRY(rt_encoder_forward_ids(e, (const int32_t*)e->ids_dev.p, nullptr, nullptr, out_dev, st));
-  RT_CHECK_CUDA(cudaMemcpyAsync(out_host, out_dev, out_bytes, cudaMemcpyDeviceToHost, st));
-  RT_CHECK_CUDA(cudaStreamSynchronize(st));
+  RT_TRY(rt_encoder_forward_ids(e, (const int32_t*)e->ids_dev.p, nullptr, nullptr, job.out.p, st));
+  RT_CHECK_CUDA(cudaEventRecord(job.computed, st));
+  RT_CHECK_CUDA(cudaStreamWaitEvent(e->copy_stream, job.computed, 0));
+  RT_CHECK_CUDA(cudaMemcpyAsync(out_host, job.out.p, out_bytes, cudaMemcpyDeviceToHost, e->copy_stream));
+  if (int* err = device_error_word())
+    RT_CHECK_CUDA(cudaMemcpyAsync(job.err_host, err, sizeof(int), cudaMemcpyDeviceToHost, e->copy_stream));
+  RT_CHECK_CUDA(cudaEventRecord(job.copied, e->copy_stream));
+  job.busy = true;
+  job.ticket = e->next_ticket;
+  *ticket = e->next_ticket++;
   return RT_OK;
+}
+
+extern "C" rt_status rt_encoder_wait_host(rt_encoder* e, uint64_t ticket) {
+  RT_REQUIRE(e != nullptr, RT_ERR_INVALID, "wait_host: null encoder");
+  RT_REQUIRE(ticket >= 1 && ticket < e->next_ticket, RT_ERR_INVALID, "wait_host: unknown ticket %llu",
+             static_cast<unsigned long long>(ticket));
+  for (auto& job : e->jobs) {
+    if (!job.busy || job.ticket != ticket) continue;
+    RT_CHECK_CUDA(cudaEventSynchronize(job.copied));
+    job.busy = false;
+    if (*job.err_host != 0)  // rt_check_device() reports the site and clears the word
+      return fail(RT_ERR_DEVICE_WAIT, "wait_host: a bounded device-side wait ran out at site %d", *job.err_host);
+    return RT_OK;
+  }
+  return RT_OK;  // already waited for (by a later submit that needed its buffer)
+}
+
+extern "C" rt_status rt_encoder_forward_host(rt_encoder* e, const int32_t* lens, int n_seq, const int32_t* ids_host,
+                                             void* out_host) {
+  uint64_t ticket = 0;
+  RT_TRY(rt_encoder_submit_host(e, lens, n_seq, ids_host, out_host, &ticket));
+  return rt_encoder_wait_host(e, ticket);
 }
 
 extern "C" rt_status rt_encoder_get_table(rt_encoder* e, int layer, const int32_t** kv_ptr, const int32_t** kv_idx,

@@ -348,12 +348,17 @@ struct ItemRef {
   AttnItem it;
 };
 
-// Cuts lists longer than `split` entries into near-equal parts; each part becomes an item of
-// its own that writes a partial result to a scratch slot.
-void split_long_items(std::vector<ItemRef>& refs, int split, AttnPlanHost& out) {
+// Cuts long lists into near-equal parts; each part becomes an item of its own that writes a
+// partial result to a scratch slot.  A list is cut only when it is longer than both `split`
+// and one CTA's fair share of the whole batch: on a large batch the longest list already fits
+// inside a CTA's share, and parts would only add partial-result traffic and a merge.
+void split_long_items(std::vector<ItemRef>& refs, int split, int n_ctas, AttnPlanHost& out) {
   out.groups.clear();
   out.n_slots = 0;
   if (split <= 0) return;
+  int64_t cost = 0;
+  for (const ItemRef& r : refs) cost += r.n_entries + 2;
+  split = std::max<int64_t>(split, (cost + n_ctas - 1) / n_ctas);
   std::vector<ItemRef> res;
   res.reserve(refs.size());
   for (const ItemRef& r : refs) {
@@ -471,7 +476,7 @@ rt_status build_attn_plan(const rt_config& cfg, const int32_t* lens, int n_seq, 
   }
   std::vector<ItemRef> refs(pend.size());
   for (size_t i = 0; i < pend.size(); ++i) refs[i] = ItemRef{pend[i].n, pool.data() + pend[i].off, pend[i].it};
-  split_long_items(refs, split_entries, out);
+  split_long_items(refs, split_entries, n_ctas, out);
   assign_and_emit(refs, n_ctas, out);
   out.total_tokens = tok0;
   out.heads = nh;
@@ -557,7 +562,7 @@ rt_status assemble_attn_plan(const rt_config& cfg, const int32_t* lens, int n_se
     out.visits += t.visits;
     tok0 += lens[s];
   }
-  split_long_items(refs, split_entries, out);
+  split_long_items(refs, split_entries, n_ctas, out);
   assign_and_emit(refs, n_ctas, out);
   out.total_tokens = tok0;
   out.heads = nh;

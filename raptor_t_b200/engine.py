@@ -98,6 +98,24 @@ class Encoder:
                                               _ptr(ids_host), _ptr(out_host)))
         return out_host
 
+    def submit_host(self, lens_tokens, ids_host, out_host):
+        """First half of forward_host: enqueues the batch and returns a ticket at once.  Up to
+        two batches are in flight; the device-to-host copy of one overlaps the kernels of the
+        next.  ids_host / out_host (pinned) must stay untouched until wait_host(ticket)."""
+        lens = np.ascontiguousarray(lens_tokens, dtype=np.int32)
+        assert not ids_host.is_cuda and ids_host.dtype == torch.int32 and not out_host.is_cuda
+        self.tokens = int(lens.sum())
+        ticket = C.c_uint64(0)
+        with torch.cuda.device(self.device):
+            check(lib.rt_encoder_submit_host(self._h, lens.ctypes.data_as(C.POINTER(C.c_int32)), len(lens),
+                                             _ptr(ids_host), _ptr(out_host), C.byref(ticket)))
+        return ticket.value
+
+    def wait_host(self, ticket):
+        """Second half: returns when the output of that batch is in its out_host buffer."""
+        with torch.cuda.device(self.device):
+            check(lib.rt_encoder_wait_host(self._h, C.c_uint64(ticket)))
+
     # ---- the three operators of the reference's pybind module -------------------------
     def attention(self, layer, x, out):
         st = C.c_void_p(torch.cuda.current_stream().cuda_stream)

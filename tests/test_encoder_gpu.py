@@ -91,6 +91,37 @@ def test_forward_host_matches_device_path_and_repeats():
         assert torch.equal(out_dev.cpu(), out_host)
 
 
+def test_host_pipeline_keeps_batches_apart():
+    """submit_host / wait_host with two batches in flight: every batch's output equals the
+    one-batch-at-a-time result, whatever the order of the waits."""
+    _skip_no_gpu()
+    cfg = EncoderConfig(hidden=128, heads=2, ffn=256, layers=2, max_pos=4096, vocab=97)
+    P = oracle.make_weights(cfg, seed=5, nonzero_bias=True)
+    enc = _make(cfg, torch.bfloat16, P)
+    batches = [[832, 1024], [64], [2048, 704, 896], [1024], [960, 64, 128]]
+    ids, outs, want = [], [], []
+    for lens in batches:
+        T = sum(lens)
+        ids.append(torch.from_numpy(np.random.default_rng(T).integers(0, cfg.vocab, size=T)).int().pin_memory())
+        outs.append(torch.zeros(T, cfg.hidden, dtype=torch.bfloat16).pin_memory())
+        want.append(enc.forward_host(lens, ids[-1], torch.empty(T, cfg.hidden, dtype=torch.bfloat16).pin_memory()).clone())
+    tickets = []
+    for i, lens in enumerate(batches):
+        tickets.append(enc.submit_host(lens, ids[i], outs[i]))
+        if i >= 1:
+            enc.wait_host(tickets[i - 1])
+            assert torch.equal(outs[i - 1], want[i - 1]), i - 1
+    enc.wait_host(tickets[-1])
+    assert torch.equal(outs[-1], want[-1])
+    enc.wait_host(tickets[0])                      # waiting twice is harmless
+    with pytest.raises(Exception):
+        enc.wait_host(tickets[-1] + 7)             # a ticket that was never issued
+    # the device-buffer entry points still work afterwards, on the caller's stream
+    enc.prepare(batches[0])
+    assert torch.equal(enc.forward_ids(ids[0].cuda()).cpu(), want[0])
+    enc.close()
+
+
 def test_operator_calls_equal_whole_layer():
     _skip_no_gpu()
     cfg = EncoderConfig(hidden=128, heads=2, ffn=256, layers=1, max_pos=4096, vocab=97)

@@ -111,7 +111,8 @@ def test_binpack_matches_oracle():
 
 
 @pytest.mark.parametrize("pattern,lens", [("bigbird", [1024, 832, 4096, 512, 704, 1984, 64, 128]),
-                                          ("band", [1280, 64, 512, 2048]), ("bigbird", [960])])
+                                          ("band", [1280, 64, 512, 2048]), ("bigbird", [960]),
+                                          ("bigbird", [4096]), ("bigbird", [2048, 4096])])
 @pytest.mark.parametrize("use_templates", [0, 1])
 def test_attention_work_list_covers_every_block_list_once(pattern, lens, use_templates):
     """Every (sequence, head, query block) appears in exactly one work item and the masked
@@ -139,8 +140,10 @@ def test_attention_work_list_covers_every_block_list_once(pattern, lens, use_tem
     slots = set()
     for q_row0, q_row1, kv_row0, off, n_ent, tok0, tok1, head_field in items.tolist():
         head, slot = head_field & 255, (head_field >> 8) - 1
-        if slot >= 0:            # one part of a split list: parts are short and own distinct scratch slots
-            assert n_ent <= 24 and slot not in slots
+        if slot >= 0:
+            # one part of a split list: no longer than 24 entries or one CTA's share of the batch,
+            # and with a scratch slot of its own
+            assert n_ent <= max(24, -(-(len(entries) + 2 * len(items)) // n_ctas)) and slot not in slots
             slots.add(slot)
         s = int(np.searchsorted(starts, tok0, side="right") - 1)
         n = lens[s]
@@ -164,6 +167,8 @@ def test_attention_work_list_covers_every_block_list_once(pattern, lens, use_tem
     assert got == expected
     visits = sum(sum(c.values()) for c in got.values())
     assert slots == set(range(len(slots)))
+    if lens in ([4096], [2048, 4096]):
+        assert len(slots) >= 2 * o.heads     # the global query blocks' lists were cut
     assert len(seen) == len(expected) and visits == plan["visits"]
     # load balance of the longest-processing-time assignment
     loads = [int(items[cta_ptr[c]:cta_ptr[c + 1], 4].sum()) for c in range(n_ctas)]
