@@ -200,11 +200,11 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       mbar_init(&sm.q_full[i], 1);
       mbar_init(&sm.q_empty[i], 1);
       mbar_init(&sm.s_full[i], 1);
-      mbar_init(&sm.s_free[i], 128);
-      mbar_init(&sm.p_full[i], 128);
+      mbar_init(&sm.s_free[i], 4);  // one elected arrival per softmax warp
+      mbar_init(&sm.p_full[i], 4);
       mbar_init(&sm.pv_done[i], 1);
     }
-    mbar_init(&sm.o_free, 128);
+    mbar_init(&sm.o_free, 4);
     for (int s = 0; s < kStagesK; ++s) {
       mbar_init(&sm.k_full[s], 1);
       mbar_init(&sm.k_empty[s], 1);
@@ -280,14 +280,23 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       volatile int* abort_flag = &sm.abort_flag;
       while ((k_g < total || v_g < total || s_g < total) && !*abort_flag) {
         bool progress = false;
+        uint64_t* gate = nullptr;  // the barrier the S issue is waiting for, if it is waiting
+        uint32_t gate_parity = 0;
         if (s_g < k_g) {
           const int rec = sm.ent_ring[s_g % kEntRing].x;
           const int qb = s_itn & 1;
           const int b = s_g & 1;
           const int st = s_g % kStagesK;
-          if ((!(rec & kEntFirst) || mbar_test_wait(&sm.q_full[qb], (s_itn >> 1) & 1)) &&
-              mbar_test_wait(&sm.k_full[st], (s_g / kStagesK) & 1) &&
-              mbar_test_wait(&sm.s_free[b], ((s_g >> 1) & 1) ^ 1)) {
+          if (!mbar_test_wait(&sm.s_free[b], ((s_g >> 1) & 1) ^ 1)) {
+            gate = &sm.s_free[b];
+            gate_parity = ((s_g >> 1) & 1) ^ 1;
+          } else if (!mbar_test_wait(&sm.k_full[st], (s_g / kStagesK) & 1)) {
+            gate = &sm.k_full[st];
+            gate_parity = (s_g / kStagesK) & 1;
+          } else if ((rec & kEntFirst) && !mbar_test_wait(&sm.q_full[qb], (s_itn >> 1) & 1)) {
+            gate = &sm.q_full[qb];
+            gate_parity = (s_itn >> 1) & 1;
+          } else {
             tc_fence_after_sync();
             const uint64_t dq = make_smem_desc_sw128(smem_u32(sm.q[qb]));
             const uint64_t dk = make_smem_desc_sw128(smem_u32(sm.k[st]));
@@ -352,7 +361,10 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         if (progress) {
           idle_since = clock64();
         } else {
-          __nanosleep(64);  // nothing to do yet (all cursors run ahead): leave the issue slots to the softmax warps
+          // nothing to do yet (all cursors run ahead): sleep on the barrier that gates the next S
+          // issue, for at most a microsecond, and leave the issue slots to the softmax warps
+          if (gate) mbar_try_wait_hint(gate, gate_parity, 1000);
+          else __nanosleep(200);
           if (clock64() - idle_since > kWaitCycles) {
             *abort_flag = 1;
             atomicCAS(error_flag, 0, 201);
@@ -438,7 +450,8 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           tc_wait_ld();
         }
         tc_fence_before_sync();
-        mbar_arrive(&sm.s_free[b]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.s_free[b]);  // one arrival per warp: 4 instead of 128 updates of the barrier word
         TRACE(12, gj)
         PROF_MARK(2)
         float alpha = 1.f;
@@ -523,7 +536,8 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         TRACE(15, gj)
         tc_wait_st();
         tc_fence_before_sync();
-        mbar_arrive(&sm.p_full[b]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.p_full[b]);
         TRACE(16, gj)
         PROF_MARK(6)
       }
@@ -558,7 +572,8 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         if (hc == 1) {
           // both halves are in registers: the MMA warp may overwrite the output tile
           tc_fence_before_sync();
-          mbar_arrive(&sm.o_free);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sm.o_free);
         }
         if (tok0 >= 0) {
           if (slot >= 0) {
