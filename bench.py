@@ -212,14 +212,33 @@ def run_gpu(args, w):
     out_pinned = torch.empty(T_local, w["hidden"], dtype=dtype).pin_memory()
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")  # > 126 MB L2
 
+    # N > 1: the all_gather of step i runs on a side stream under the kernels of the next two
+    # steps (three output buffers rotate), so that the ranks are coupled loosely: a step's timed
+    # window ends after the gather issued two steps earlier has finished, and the tail of the
+    # last gathers is added to the total.
+    DEPTH = 3
+    gatherer = (parallel.OutputGatherer(assignment, lens_all, w["hidden"], dtype, "cuda", depth=DEPTH)
+                if n_gpus > 1 else None)
+    out_devs = [out_dev] + [torch.empty_like(out_dev) for _ in range(DEPTH - 1)]
+    pipe = {"i": 0, "pending": []}
+
     def step():
+        k = pipe["i"] % DEPTH
+        pipe["i"] += 1
         enc.prepare(lens)
-        enc.forward_ids(ids_dev, out=out_dev)
-        if n_gpus > 1:
-            return parallel.gather_outputs(out_dev, assignment, lens_all)
-        return out_dev
+        enc.forward_ids(ids_dev, out=out_devs[k])
+        if gatherer is not None:
+            pipe["pending"].append(gatherer.start(out_devs[k]))
+            if len(pipe["pending"]) >= DEPTH:
+                gatherer.finish(pipe["pending"].pop(0))
+        return out_devs[k]
+
+    def drain():
+        while gatherer is not None and pipe["pending"]:
+            gatherer.finish(pipe["pending"].pop(0))
 
     def barrier():
+        drain()
         torch.cuda.synchronize()
         if n_gpus > 1:
             dist.barrier()
@@ -238,14 +257,19 @@ def run_gpu(args, w):
     sampler = ClockSampler(local_rank) if rank == 0 else None
     launches0 = kernel_launches()
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    host_t0 = time.perf_counter()
     for a, b in ev:
         flush.fill_(1)
         a.record()
         step()
         b.record()
+    host_ms_per_step = (time.perf_counter() - host_t0) * 1e3 / args.steps  # launch time only: nothing waits here
+    tail = torch.cuda.Event(enable_timing=True)
+    drain()
+    tail.record()
     barrier()
     launches = kernel_launches() - launches0
-    t_ms = sum(a.elapsed_time(b) for a, b in ev)
+    t_ms = sum(a.elapsed_time(b) for a, b in ev) + ev[-1][1].elapsed_time(tail)
     t = torch.tensor([t_ms], dtype=torch.float64, device="cuda")
     if n_gpus > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -352,7 +376,8 @@ def run_gpu(args, w):
                    "l2": "flushed between timed steps (256 MiB write)",
                    "stage_timing": "per-kernel durations (roofline, stages_ms_per_step) come from a second pass of the "
                                    "same steps with CUDA events around every launch",
-                   "parallelism": f"replicas x{n_gpus}, whole-sequence bin packing, all_gather of outputs timed"
+                   "parallelism": f"replicas x{n_gpus}, whole-sequence bin packing, all_gather of outputs timed (the gather of "
+                                  f"step i overlaps the kernels of steps i+1 and i+2; the last gathers' tail is added)"
                    if n_gpus > 1 else "single GPU"},
         "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms_per_step, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h,
@@ -360,6 +385,7 @@ def run_gpu(args, w):
                         "D2H copies are inside the timed region",
                 "one_batch_at_a_time_ms_per_step": e2e_sync_ms},
         "gpu_launches": int(launches),
+        "host_launch_ms_per_step": host_ms_per_step,
         "clocks": clocks,
         "roofline": roof,
         "stages_ms_per_step": per,
@@ -383,9 +409,13 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="base", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--seqs", type=int, default=0, help="sequences per GPU (default: the workload's own count)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     w = WORKLOADS[args.workload]
+    if args.seqs > 0:
+        w["seqs"] = args.seqs
+        w["desc"] += f" (--seqs {args.seqs})"
     if args.impl == "reference":
         run_reference(args, w)
     else:

@@ -56,3 +56,74 @@ def unpermute(per_rank, assignment, lens_tokens):
             out[starts[i]: starts[i] + n] = per_rank[r, off: off + n]
             off += n
     return out
+
+
+def gather_permutation(assignment, lens_tokens, pad):
+    """Row index into the gathered [world * pad, H] buffer for every output row (input order)."""
+    starts = np.concatenate([[0], np.cumsum(lens_tokens)]).astype(np.int64)
+    perm = np.empty(int(starts[-1]), dtype=np.int64)
+    for r, seqs in enumerate(assignment):
+        off = 0
+        for i in seqs:
+            n = int(lens_tokens[i])
+            perm[starts[i]: starts[i] + n] = r * pad + off + np.arange(n, dtype=np.int64)
+            off += n
+    return perm
+
+
+class OutputGatherer:
+    """The gather of one batch layout with everything set up once: padded send buffer,
+    receive buffers, the row permutation on the device.  gather() costs one all_gather and
+    one index_select.  On CUDA the two run on a side stream (start()/finish()), so a caller
+    that keeps two batches in flight overlaps the gather of one with the kernels of the next;
+    `depth` result buffers rotate."""
+
+    def __init__(self, assignment, lens_tokens, hidden, dtype, device, group=None, depth=2):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        tokens_of = [sum(int(lens_tokens[i]) for i in assignment[r]) for r in range(self.world)]
+        self.pad, self.local_tokens, self.total = max(tokens_of), tokens_of[self.rank], int(sum(tokens_of))
+        self.device = torch.device(device)
+        self.perm = torch.from_numpy(gather_permutation(assignment, lens_tokens, self.pad)).to(self.device)
+        self.send = [torch.zeros(self.pad, hidden, dtype=dtype, device=self.device) for _ in range(depth)]
+        self.recv = [torch.empty(self.world * self.pad, hidden, dtype=dtype, device=self.device) for _ in range(depth)]
+        self.out = [torch.empty(self.total, hidden, dtype=dtype, device=self.device) for _ in range(depth)]
+        self.cuda = self.device.type == "cuda"
+        self.side = torch.cuda.Stream(device=self.device) if self.cuda else None
+        self.done = [torch.cuda.Event() for _ in range(depth)] if self.cuda else None
+        self.n = 0
+
+    def _run(self, local_out, k):
+        self.send[k][: self.local_tokens].copy_(local_out)
+        dist.all_gather_into_tensor(self.recv[k], self.send[k], group=self.group)
+        torch.index_select(self.recv[k], 0, self.perm, out=self.out[k])
+        return self.out[k]
+
+    def gather(self, local_out):
+        """Synchronous with the current stream: returns the [T_total, H] tensor in input order."""
+        k = self.n % len(self.out)
+        self.n += 1
+        return self._run(local_out, k)
+
+    def start(self, local_out):
+        """Enqueue the gather behind the work already on the current stream, on the side
+        stream; returns a ticket for finish().  local_out must stay untouched until then."""
+        k = self.n % len(self.out)
+        self.n += 1
+        if not self.cuda:
+            self._run(local_out, k)
+            return k
+        ready = torch.cuda.Event()
+        ready.record()
+        with torch.cuda.stream(self.side):
+            self.side.wait_event(ready)
+            self._run(local_out, k)
+            self.done[k].record()
+        return k
+
+    def finish(self, ticket):
+        """Makes the current stream wait for that gather and returns its result buffer."""
+        if self.cuda:
+            torch.cuda.current_stream().wait_event(self.done[ticket])
+        return self.out[ticket]

@@ -31,6 +31,12 @@ def _worker(rank, world, port, lens, H):
     exp = torch.cat([(1000.0 * i + torch.arange(n, dtype=torch.float32)[:, None] / 4096).expand(n, H)
                      for i, n in enumerate(lens)], 0)
     assert torch.equal(full, exp)
+    # the set-up-once gatherer: same result through gather() and through start()/finish(), twice
+    g = parallel.OutputGatherer(assignment, lens, H, torch.float32, "cpu")
+    assert torch.equal(g.gather(local), exp)
+    t1 = g.start(local)
+    t2 = g.start(local * 2)
+    assert torch.equal(g.finish(t1), exp) and torch.equal(g.finish(t2), exp * 2)
     dist.destroy_process_group()
 
 
