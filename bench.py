@@ -343,7 +343,7 @@ def run_gpu(args, w):
     tr_gbs = (w["layers"] * 2 * T_local * 3 * w["hidden"] * 2) / (tr_ms * 1e-3) / 1e9 if tr_ms else 0.0
     dominant_is_gemm = gemm_ms >= attn_ms
     if dominant_is_gemm:
-        roof = {"kernel": "gemm_kernel (tcgen05 projection GEMMs, 4 per layer)", "bound": "tensor",
+        roof = {"kernel": "gemm_pair_kernel (CTA-pair tcgen05 projection GEMMs, 4 per layer)", "bound": "tensor",
                 "achieved": gemm_tf, "peak": pk["tf_sustained"], "unit": "TFLOP/s",
                 "frac": gemm_tf / pk["tf_sustained"], "traffic": ncu_traffic("gemm", gemm_fl / n_gemm),
                 "launches_per_step": n_gemm, "avg_launch_ms": gemm_ms / n_gemm,
