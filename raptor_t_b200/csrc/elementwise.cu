@@ -351,7 +351,9 @@ static rt_status layernorm_launch(void* out, const void* x, const void* bias, co
                                   const void* beta, int rows, int hidden, float eps, cudaStream_t st) {
   const int nv = (hidden / 8 + 31) / 32;
   const int threads = 256, wpb = threads / 32;
-  int blocks = std::min((rows + wpb - 1) / wpb, sm_count() * 16);
+  // at most two waves of resident CTAs (3 per SM); warps walk the rows with a grid stride, so the
+  // parameters are staged in shared memory a few times per SM instead of once per 8 rows
+  int blocks = std::min((rows + wpb - 1) / wpb, sm_count() * 6);
   if (blocks < 1) blocks = 1;
 #define RT_LN_CASE(NV)                                                                                           \
   case NV:                                                                                                       \
