@@ -76,6 +76,31 @@ def test_base_encoder_hidden_states_within_tolerance():
         enc.close()
 
 
+def test_large_shape_layers_within_tolerance():
+    """BigBird-large dimensions (hidden 1024, 16 heads, FFN 4096, 8192 positions), two layers, a
+    batch with a sparse, a full-attention and a long sequence: every GEMM shape, the 1024-wide
+    LayerNorm and 16-head attention of that model against the oracle."""
+    _skip_no_gpu()
+    cfg = EncoderConfig(hidden=1024, heads=16, ffn=4096, layers=2, max_pos=8192, vocab=500)
+    P = oracle.make_weights(cfg, seed=7, nonzero_bias=True)
+    lens = [1088, 640, 5120]
+    rng = np.random.default_rng(1)
+    seqs = [torch.from_numpy(rng.integers(0, cfg.vocab, size=n)).int() for n in lens]
+    ref = oracle.encoder_ref(seqs, P, cfg)
+    enc = _make(cfg, torch.bfloat16, P)
+    enc.prepare(lens)
+    out = enc.forward_ids(torch.cat(seqs).cuda())
+    from raptor_t_b200 import ops
+    ops.check_device()
+    err = (out.float().cpu() - ref).abs()
+    assert err.max().item() < 8e-2 and err.mean().item() < 8e-3, (err.max().item(), err.mean().item())
+    for layer in range(cfg.layers):
+        ptr, idx = enc.table(layer)
+        optr, oidx = oracle.build_block_csr(lens, cfg, layer)
+        assert np.array_equal(ptr, optr) and np.array_equal(idx, oidx)
+    enc.close()
+
+
 def test_forward_host_matches_device_path_and_repeats():
     _skip_no_gpu()
     cfg = EncoderConfig(hidden=128, heads=2, ffn=256, layers=2, max_pos=4096, vocab=97)
