@@ -363,12 +363,12 @@ rt_status run_attention(rt_encoder* e, int l, const void* input, void* output, c
   void* dense = e->scratch["dense_out"].p;
   RT_CHECK_CUDA(cudaStreamWaitEvent(st, e->cur->prefix_ready, 0));
   if (e->fuse_qkv) {
-    Span s(e, st, "gemm");
+    Span s(e, st, "gemm.qkv");
     const int32_t* block_seq = static_cast<const int32_t*>(e->cur->prefix_dev.p) + e->cur->block_seq_off;
     RT_TRY(rt_gemm_qkv(q, k, v, input, w.qkv_w.p, w.qkv_b.p, block_seq, T, c.heads, H, 0.125f, dt, st));
   } else {
     {
-      Span s(e, st, "gemm");
+      Span s(e, st, "gemm.qkv");
       RT_TRY(rt_gemm(qkv, input, w.qkv_w.p, nullptr, T, 3 * H, H, RT_EPI_NONE, dt, st));
     }
     Span s(e, st, "add_bias_and_transpose_kernel");
@@ -388,14 +388,14 @@ rt_status run_attention(rt_encoder* e, int l, const void* input, void* output, c
   }
   if (e->fuse_residual) {
     {
-      Span s(e, st, "gemm");
+      Span s(e, st, "gemm.attention_output");
       RT_TRY(rt_gemm_residual(dense, ctx, w.ao_w.p, w.ao_b.p, input, T, H, H, dt, st));
     }
     Span s(e, st, "add_bias_and_layernorm_kernel");
     RT_TRY(rt_bias_residual_layernorm(output, dense, nullptr, nullptr, w.aln_g.p, w.aln_b.p, T, H, c.eps, dt, st));
   } else {
     {
-      Span s(e, st, "gemm");
+      Span s(e, st, "gemm.attention_output");
       RT_TRY(rt_gemm(dense, ctx, w.ao_w.p, nullptr, T, H, H, RT_EPI_NONE, dt, st));
     }
     Span s(e, st, "add_bias_and_layernorm_kernel");
@@ -409,11 +409,11 @@ rt_status run_intermediate(rt_encoder* e, int l, const void* input, void* output
   LayerWeights& w = e->layers[l];
   RT_REQUIRE(w.set, RT_ERR_STATE, "layer %d has no weights", l);
   if (e->fuse_gelu) {
-    Span s(e, st, "gemm");
+    Span s(e, st, "gemm.ffn_up");
     RT_TRY(rt_gemm(output, input, w.up_w.p, w.up_b.p, e->tokens, c.ffn, c.hidden, RT_EPI_BIAS_GELU, c.dtype, st));
   } else {
     {
-      Span s(e, st, "gemm");
+      Span s(e, st, "gemm.ffn_up");
       RT_TRY(rt_gemm(output, input, w.up_w.p, nullptr, e->tokens, c.ffn, c.hidden, RT_EPI_NONE, c.dtype, st));
     }
     Span s(e, st, "add_bias_act_kernel");
@@ -429,7 +429,7 @@ rt_status run_output(rt_encoder* e, int l, const void* ffn, const void* residual
   void* dense = e->scratch["dense_out"].p;
   if (e->fuse_residual) {
     {
-      Span s(e, st, "gemm");
+      Span s(e, st, "gemm.ffn_down");
       RT_TRY(rt_gemm_residual(dense, ffn, w.down_w.p, w.down_b.p, residual, e->tokens, c.hidden, c.ffn, c.dtype, st));
     }
     Span s(e, st, "add_bias_and_layernorm_kernel");
@@ -438,7 +438,7 @@ rt_status run_output(rt_encoder* e, int l, const void* ffn, const void* residual
     return RT_OK;
   }
   {
-    Span s(e, st, "gemm");
+    Span s(e, st, "gemm.ffn_down");
     RT_TRY(rt_gemm(dense, ffn, w.down_w.p, nullptr, e->tokens, c.hidden, c.ffn, RT_EPI_NONE, c.dtype, st));
   }
   Span s(e, st, "add_bias_and_layernorm_kernel");
@@ -868,8 +868,11 @@ extern "C" rt_status rt_encoder_get_timing(rt_encoder* e, const char* key, float
   }
   RT_CHECK_CUDA(cudaDeviceSynchronize());
   float total = 0.f;
+  const size_t klen = std::strlen(key);
   for (auto& s : e->timer.spans) {
-    if (s.first != key) continue;
+    // "gemm" also collects "gemm.qkv", "gemm.ffn_up", ...
+    const bool sub = s.first.size() > klen && s.first.compare(0, klen, key) == 0 && s.first[klen] == '.';
+    if (s.first != key && !sub) continue;
     float ms = 0.f;
     if (cudaEventElapsedTime(&ms, s.second.first, s.second.second) == cudaSuccess) total += ms;
   }

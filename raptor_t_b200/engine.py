@@ -151,7 +151,8 @@ class Encoder:
 
     def timing(self):
         out = {}
-        for key in ("gemm", "add_bias_and_transpose_kernel", "attention", "add_bias_and_layernorm_kernel",
+        for key in ("gemm", "gemm.qkv", "gemm.attention_output", "gemm.ffn_up", "gemm.ffn_down",
+                    "add_bias_and_transpose_kernel", "attention", "add_bias_and_layernorm_kernel",
                     "add_bias_act_kernel", "embeddings", "pre_process"):
             ms = C.c_float()
             check(lib.rt_encoder_get_timing(self._h, key.encode(), C.byref(ms)))
