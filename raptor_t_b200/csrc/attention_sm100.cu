@@ -10,7 +10,9 @@
 //            per item and of one K box and one V box (64 x 64, 128-byte swizzle) per
 //            list entry into two shared-memory rings, and the issue of S = Q K^T
 //            (M=128, N=64, K=64; both operands K-major in shared memory) into one of
-//            two TMEM score buffers as soon as its K block has landed;
+//            two TMEM score buffers as soon as its K block has landed.  It reads the
+//            work list ahead with asynchronous 4-byte copies and hands one record per
+//            entry to the other warps through a shared-memory ring;
 //   warp 5   one thread issues PV = P V (P read from TMEM, V MN-major in shared
 //            memory), accumulating the output tile in TMEM.  Splitting the two MMA
 //            issue chains over two threads matters: each chain (barrier polls, four
@@ -24,8 +26,12 @@
 //            then at most 256, well inside 16-bit range), and read once per item
 //            for the final division by the row sum.
 //
-// Two CTAs share an SM (256 TMEM columns and ~97 KB of shared memory each), so one
+// Two CTAs share an SM (256 TMEM columns and ~107 KB of shared memory each), so one
 // CTA's softmax latency hides behind the other's.
+//
+// Lists that are longer than one CTA's share of the batch are cut into parts by the
+// host; a part leaves its un-normalised fp32 output tile, row maxima and row sums in
+// scratch and merge_partials_kernel combines the parts of a list.
 //
 // Output rows go token-major [T][heads*64].  Counterpart of
 // layers/kernels/sparse_attention.cu:2953-3228; the math follows the reference's
@@ -148,8 +154,6 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
   }
 }
 
-// Optional phase timing (compiled in only with -DRT_ATTN_PROFILE, for tuning): lane 0 of
-// every warp adds the SM clocks it spends in each phase to a global table.
 #ifdef RT_ATTN_TRACE
 // Tuning builds only: lane 0 of every warp of CTA 0 logs (clock, event, index) into its own
 // slice with plain stores.
@@ -165,17 +169,6 @@ __device__ unsigned long long g_trace[8 * 1024 * 2];
 #else
 #define TRACE_DECL
 #define TRACE(ev, idx)
-#endif
-#ifdef RT_ATTN_PROFILE
-__device__ unsigned long long g_attn_prof[16];
-__device__ unsigned long long g_attn_cta_log[1024 * 3];  // per CTA: sm id, start ns, end ns
-#define PROF_DECL long long _pt = clock64(); unsigned long long _pb[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#define PROF_MARK(i) { long long _n = clock64(); _pb[i] += (unsigned long long)(_n - _pt); _pt = _n; }
-#define PROF_FLUSH(base) { if ((threadIdx.x & 31) == 0) for (int _i = 0; _i < 8; ++_i) if (_pb[_i]) atomicAdd(&g_attn_prof[(base) + _i], _pb[_i]); }
-#else
-#define PROF_DECL
-#define PROF_MARK(i)
-#define PROF_FLUSH(base)
 #endif
 
 template <bool BF16>
@@ -230,16 +223,6 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   const int item_begin = cta_ptr[blockIdx.x];
   const int item_end = cta_ptr[blockIdx.x + 1];
   TRACE_DECL
-#ifdef RT_ATTN_PROFILE
-  if (threadIdx.x == 0 && blockIdx.x < 1024) {
-    unsigned smid;
-    unsigned long long t;
-    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    g_attn_cta_log[blockIdx.x * 3] = smid;
-    g_attn_cta_log[blockIdx.x * 3 + 1] = t;
-  }
-#endif
 
   if (warp == 4) {
     // ------------------------------------------------------------------ TMA producer
@@ -422,7 +405,6 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
     uint32_t g = 0, itn = 0;
     bool ok = true;
-    PROF_DECL
     AttnItem next_item = item_begin < item_end ? items[item_begin] : AttnItem{};
     for (int it = item_begin; it < item_end && ok; ++it) {
       const AttnItem item = next_item;
@@ -435,11 +417,9 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         const uint32_t gj = g + j;
         const int b = gj & 1;
         const uint32_t u = gj >> 1;
-        PROF_MARK(0)
         TRACE(10, gj)
         if (!mbar_wait(&sm.s_full[b], u & 1, ab, 221)) { ok = false; break; }
         TRACE(11, gj)
-        PROF_MARK(1)
         tc_fence_after_sync();
         // the producer published this entry's record before it loaded the K block of the S tile just waited for
         const bool active = ((sm.ent_ring[gj % kEntRing].x >> half) & 1) != 0;
@@ -453,7 +433,6 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm.s_free[b]);  // one arrival per warp: 4 instead of 128 updates of the barrier word
         TRACE(12, gj)
-        PROF_MARK(2)
         float alpha = 1.f;
         bool fix = false;
         if (active) {
@@ -479,11 +458,9 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         }
         // the probability buffer was last read by the PV MMA two entries back
         if (gj >= 2) {
-          PROF_MARK(3)
           TRACE(13, gj)
           if (!mbar_wait(&sm.pv_done[b], ((gj - 2) >> 1) & 1, ab, 222)) { ok = false; break; }
           TRACE(14, gj)
-          PROF_MARK(4)
         }
         if (__any_sync(0xffffffffu, fix)) {
           // rescale this warp's rows of the output tile; every PV MMA issued so far must be done
@@ -532,25 +509,21 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           tmem_st16(lane_base + kColP + b * 32, p);
           tmem_st16(lane_base + kColP + b * 32 + 16, p);
         }
-        PROF_MARK(5)
         TRACE(15, gj)
         tc_wait_st();
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm.p_full[b]);
         TRACE(16, gj)
-        PROF_MARK(6)
       }
       if (!ok) break;
       g += n;
       // final: the last PV MMA of the item completes the output tile
       {
         const uint32_t gl = g - 1;
-        PROF_MARK(0)
         TRACE(17, gl)
         if (!mbar_wait(&sm.pv_done[gl & 1], (gl >> 1) & 1, ab, 224)) { ok = false; break; }
         TRACE(18, gl)
-        PROF_MARK(7)
         tc_fence_after_sync();
       }
       const int tok0 = half == 0 ? item.out_tok0 : item.out_tok1;
@@ -595,17 +568,8 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       ++itn;
     }
     (void)itn;
-    PROF_MARK(0)
-    PROF_FLUSH(0)
   }
 
-#ifdef RT_ATTN_PROFILE
-  if (threadIdx.x == 0 && blockIdx.x < 1024) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    g_attn_cta_log[blockIdx.x * 3 + 2] = t;
-  }
-#endif
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 5) {
@@ -827,23 +791,6 @@ extern "C" rt_status rt_attn_trace_read(unsigned long long* out, int reset) {
   RT_CHECK_CUDA(cudaDeviceSynchronize());
   RT_CHECK_CUDA(cudaMemcpyFromSymbol(out, rt::g_trace, sizeof(unsigned long long) * 2 * 8 * 1024));
   if (reset) RT_CHECK_CUDA(cudaMemset([] { void* p; cudaGetSymbolAddress(&p, rt::g_trace); return p; }(), 0, sizeof(unsigned long long) * 2 * 8 * 1024));
-  return RT_OK;
-}
-#endif
-#ifdef RT_ATTN_PROFILE
-// Tuning builds only: read (and optionally clear) the phase-clock table.
-extern "C" rt_status rt_attn_cta_log_read(unsigned long long* out, int n_ctas) {
-  RT_CHECK_CUDA(cudaDeviceSynchronize());
-  RT_CHECK_CUDA(cudaMemcpyFromSymbol(out, rt::g_attn_cta_log, sizeof(unsigned long long) * 3 * n_ctas));
-  return RT_OK;
-}
-extern "C" rt_status rt_attn_profile_read(unsigned long long* out16, int reset) {
-  RT_CHECK_CUDA(cudaDeviceSynchronize());
-  RT_CHECK_CUDA(cudaMemcpyFromSymbol(out16, rt::g_attn_prof, sizeof(unsigned long long) * 16));
-  if (reset) {
-    unsigned long long z[16] = {0};
-    RT_CHECK_CUDA(cudaMemcpyToSymbol(rt::g_attn_prof, z, sizeof(z)));
-  }
   return RT_OK;
 }
 #endif
