@@ -6,17 +6,20 @@
 // random blocks come from the same table; each entry carries a 2-bit mask that
 // says which of the two query blocks uses it).
 //
-//   warp 4   one thread runs a polling loop over three jobs: TMA loads of the Q tile
-//            per item and of one K box and one V box (64 x 64, 128-byte swizzle) per
-//            list entry into two shared-memory rings, and the issue of S = Q K^T
-//            (M=128, N=64, K=64; both operands K-major in shared memory) into one of
-//            two TMEM score buffers as soon as its K block has landed.  It reads the
-//            work list ahead with asynchronous 4-byte copies and hands one record per
-//            entry to the other warps through a shared-memory ring;
-//   warp 5   one thread issues PV = P V (P read from TMEM, V MN-major in shared
-//            memory), accumulating the output tile in TMEM.  Splitting the two MMA
-//            issue chains over two threads matters: each chain (barrier polls, four
-//            K=16 MMAs, commits) costs about a thousand clocks per entry;
+// Four warps contribute one thread each, with blocking (bounded) waits on their own
+// barriers, so that their serial latencies run side by side:
+//   warp 4   K / Q loader: TMA loads of the Q tile per item and of one K box (64 x 64,
+//            128-byte swizzle) per list entry into a shared-memory ring.  The only role
+//            that reads the work list in global memory (4-byte asynchronous copies, eight
+//            entries ahead); it publishes one record per entry ({entry, first/last flags,
+//            key/value row}) in a shared-memory ring for the other roles;
+//   warp 6   V loader: one V box per entry into its own ring;
+//   warp 7   issues S = Q K^T (M=128, N=64, K=64; both operands K-major in shared memory)
+//            into one of two TMEM score buffers, as soon as the K block has landed and the
+//            PV MMA two entries back has completed (which frees score buffer and
+//            probability buffer of that parity at once);
+//   warp 5   issues PV = P V (P read from TMEM, V MN-major in shared memory), accumulating
+//            the output tile in TMEM;
 //   warps 0-3  softmax: thread r owns tile row r.  It pulls its score row out of
 //            TMEM, keeps the running max / sum in fp32 (base-2 exponentials) and
 //            writes the 16-bit probabilities back to TMEM for the PV MMA.  The
@@ -24,7 +27,10 @@
 //            add into it); it is rescaled only when a row's max has grown by more
 //            than 2^8 since the last rescale ("lazy" rescaling: probabilities are
 //            then at most 256, well inside 16-bit range), and read once per item
-//            for the final division by the row sum.
+//            for the final division by the row sum.  One barrier wait (score tile
+//            ready) and one arrival (probabilities stored) per entry.
+// The kernel is launched with 128 registers per thread; the issue warps hand registers
+// to the softmax warps (setmaxnreg 72 / 184), which hold a 64-column score row each.
 //
 // Two CTAs share an SM (256 TMEM columns and ~107 KB of shared memory each), so one
 // CTA's softmax latency hides behind the other's.
@@ -57,7 +63,7 @@ namespace {
 
 using namespace ptx;
 
-constexpr int kThreads = 192;
+constexpr int kThreads = 256;  // warps 0-3 softmax; 4: K/Q loads, 5: PV issue, 6: V loads, 7: S issue (one thread each)
 constexpr int kStagesK = 4;              // K ring depth (a slot is free again once the S MMA has read it)
 constexpr int kStagesV = 5;              // V ring depth (a slot is held until the PV MMA, two softmax periods later)
 constexpr int kEntRing = 32;             // per-entry records travel from the K cursor to the other roles through smem
@@ -79,11 +85,12 @@ struct Smem {
   uint8_t v[kStagesV][kTileBytes];
   uint64_t q_full[2], q_empty[2];
   uint64_t k_full[kStagesK], k_empty[kStagesK], v_full[kStagesV], v_empty[kStagesV];
-  uint64_t s_full[2], s_free[2], p_full[2], pv_done[2], o_free;
+  uint64_t s_full[2], p_full[2], pv_done[2], o_free;
   int2 ent_ring[kEntRing];      // {entry (block << 2 | mask) | flags, row of the key/value block}
   int32_t ent_stage[kEntStage];
   uint32_t tmem_slot;
   int abort_flag;
+  uint32_t k_published;  // entry records written so far (K loader -> V loader)
 };
 constexpr int kSmemBytes = sizeof(Smem);
 
@@ -171,8 +178,22 @@ __device__ unsigned long long g_trace[8 * 1024 * 2];
 #define TRACE(ev, idx)
 #endif
 
+// Register budget: the kernel is launched with 128 registers per thread (two CTAs of 256
+// threads per SM); the four single-thread warps then give registers back and the softmax
+// warps, which hold a 64-column score row per thread, take them.
+constexpr int kRegsIssue = 72;
+constexpr int kRegsSoftmax = 184;
+template <int N>
+__device__ __forceinline__ void reg_dealloc() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_alloc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+
 template <bool BF16>
-__global__ void __maxnreg__(160)
+__global__ void __launch_bounds__(kThreads, 2)
 sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, uint16_t* __restrict__ ctx,
                         const AttnItem* __restrict__ items, const int32_t* __restrict__ entries,
@@ -193,8 +214,7 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       mbar_init(&sm.q_full[i], 1);
       mbar_init(&sm.q_empty[i], 1);
       mbar_init(&sm.s_full[i], 1);
-      mbar_init(&sm.s_free[i], 4);  // one elected arrival per softmax warp
-      mbar_init(&sm.p_full[i], 4);
+      mbar_init(&sm.p_full[i], 4);  // one elected arrival per softmax warp
       mbar_init(&sm.pv_done[i], 1);
     }
     mbar_init(&sm.o_free, 4);
@@ -207,6 +227,7 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       mbar_init(&sm.v_empty[s], 1);
     }
     sm.abort_flag = 0;
+    sm.k_published = 0;
     fence_barrier_init();
   }
   if (warp == 5) {
@@ -224,19 +245,20 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   const int item_end = cta_ptr[blockIdx.x + 1];
   TRACE_DECL
 
+  // Four single-thread roles walk the CTA's flattened (item, entry) stream, each with blocking
+  // (bounded) waits on its own barriers, so that their serial latencies (barrier round trips,
+  // descriptor set-up, TMA / MMA issue, commits: several hundred clocks per entry each) run
+  // side by side instead of adding up in one thread.
+  if (warp >= 4) {
+  reg_dealloc<kRegsIssue>();  // executed by all four warps of the upper warpgroup at this one place
   if (warp == 4) {
-    // ------------------------------------------------------------------ TMA producer
-    // One thread walks the CTA's flattened (item, entry) stream with three cursors: K loads
-    // (which also load each item's Q tile and publish one record per entry), V loads and the
-    // S = Q K^T issue.  Only the K cursor touches the work list in global memory: the entries
-    // arrive through asynchronous copies issued kEntAhead entries early and the next item is
-    // prefetched in registers, so no cursor ever waits on a global load.  The V and S cursors
-    // (and the PV and softmax warps) take what they need from the records in shared memory.
+    // ------------------------------------------------------------------ K / Q loader
+    // The only role that reads the work list in global memory: entries arrive through 4-byte
+    // asynchronous copies issued kEntAhead entries early, the next item is prefetched in
+    // registers.  It publishes one record per entry for the other roles.
     if (lane == 0) {
       prefetch_tensormap(&map_q);
       prefetch_tensormap(&map_k);
-      prefetch_tensormap(&map_v);
-      constexpr uint32_t idesc_s = make_idesc_f16(128, 64, BF16 ? 1 : 0, false);
       int ent_first;
       uint32_t total;
       cta_entry_range(items, item_begin, item_end, ent_first, total);
@@ -247,7 +269,7 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       };
       for (uint32_t i = 0; i < kEntAhead; ++i) fetch(i);
       int k_item = item_begin, k_j = 0;
-      uint32_t k_g = 0, v_g = 0, s_g = 0, k_itn = 0, s_itn = 0;
+      uint32_t k_itn = 0;
       AttnItem ki{}, kn{};
       auto settle_item = [&]() {  // k_item -> first item with a non-empty list; prefetch the one after it
         while (k_item < item_end && ki.n_entries == 0) {
@@ -258,105 +280,107 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       };
       if (k_item < item_end) ki = items[k_item];
       settle_item();
-      bool q_loaded = false;
-      long long idle_since = clock64();
-      volatile int* abort_flag = &sm.abort_flag;
-      while ((k_g < total || v_g < total || s_g < total) && !*abort_flag) {
-        bool progress = false;
-        uint64_t* gate = nullptr;  // the barrier the S issue is waiting for, if it is waiting
-        uint32_t gate_parity = 0;
-        if (s_g < k_g) {
-          const int rec = sm.ent_ring[s_g % kEntRing].x;
-          const int qb = s_itn & 1;
-          const int b = s_g & 1;
-          const int st = s_g % kStagesK;
-          if (!mbar_test_wait(&sm.s_free[b], ((s_g >> 1) & 1) ^ 1)) {
-            gate = &sm.s_free[b];
-            gate_parity = ((s_g >> 1) & 1) ^ 1;
-          } else if (!mbar_test_wait(&sm.k_full[st], (s_g / kStagesK) & 1)) {
-            gate = &sm.k_full[st];
-            gate_parity = (s_g / kStagesK) & 1;
-          } else if ((rec & kEntFirst) && !mbar_test_wait(&sm.q_full[qb], (s_itn >> 1) & 1)) {
-            gate = &sm.q_full[qb];
-            gate_parity = (s_itn >> 1) & 1;
-          } else {
-            tc_fence_after_sync();
-            const uint64_t dq = make_smem_desc_sw128(smem_u32(sm.q[qb]));
-            const uint64_t dk = make_smem_desc_sw128(smem_u32(sm.k[st]));
-            const uint32_t d = tmem_base + kColS + b * 64;
-#pragma unroll
-            for (int k = 0; k < 4; ++k) mma_ss(d, dq + (k * 32 >> 4), dk + (k * 32 >> 4), idesc_s, k ? 1u : 0u);
-            tc_commit(&sm.k_empty[st]);
-            tc_commit(&sm.s_full[b]);
-            TRACE(5, s_g)
-            ++s_g;
-            if (rec & kEntLast) {
-              tc_commit(&sm.q_empty[qb]);
-              ++s_itn;
-            }
-            progress = true;
-          }
-        }
-        if (k_g < total) {
+      bool ok = true;
+      for (uint32_t k_g = 0; ok && k_g < total; ++k_g) {
+        if (k_j == 0) {
           const int qb = k_itn & 1;
-          if (!q_loaded && mbar_test_wait(&sm.q_empty[qb], ((k_itn >> 1) & 1) ^ 1)) {
-            mbar_arrive_expect_tx(&sm.q_full[qb], kQBytes);
-            tma_load_2d(sm.q[qb], &map_q, 0, ki.q_row0, &sm.q_full[qb]);
-            tma_load_2d(sm.q[qb] + kTileBytes, &map_q, 0, ki.q_row1, &sm.q_full[qb]);
-            q_loaded = true;
-            progress = true;
-          }
-          const int s = k_g % kStagesK;
-          if (q_loaded && mbar_test_wait(&sm.k_empty[s], ((k_g / kStagesK) & 1) ^ 1)) {
-            cp_async_wait<kEntAhead - 1>();  // the copy of entry k_g has landed
-            const int e = *reinterpret_cast<volatile int32_t*>(&sm.ent_stage[k_g % kEntStage]);
-            fetch(k_g + kEntAhead);
-            const int row = ki.kv_row0 + (e >> 2) * 64;
-            const bool last = k_j + 1 == ki.n_entries;
-            sm.ent_ring[k_g % kEntRing] = make_int2(e | (k_j == 0 ? kEntFirst : 0) | (last ? kEntLast : 0), row);
-            mbar_arrive_expect_tx(&sm.k_full[s], kTileBytes);
-            tma_load_2d(sm.k[s], &map_k, 0, row, &sm.k_full[s]);
-            TRACE(1, k_g)
-            ++k_g;
-            ++k_j;
-            if (last) {
-              ++k_item;
-              ++k_itn;
-              k_j = 0;
-              q_loaded = false;
-              ki = kn;
-              settle_item();
-            }
-            progress = true;
-          }
+          if (!mbar_wait(&sm.q_empty[qb], ((k_itn >> 1) & 1) ^ 1, ab, 211)) break;
+          mbar_arrive_expect_tx(&sm.q_full[qb], kQBytes);
+          tma_load_2d(sm.q[qb], &map_q, 0, ki.q_row0, &sm.q_full[qb]);
+          tma_load_2d(sm.q[qb] + kTileBytes, &map_q, 0, ki.q_row1, &sm.q_full[qb]);
         }
-        if (v_g < k_g) {
-          const int s = v_g % kStagesV;
-          if (mbar_test_wait(&sm.v_empty[s], ((v_g / kStagesV) & 1) ^ 1)) {
-            const int row = sm.ent_ring[v_g % kEntRing].y;
-            mbar_arrive_expect_tx(&sm.v_full[s], kTileBytes);
-            tma_load_2d(sm.v[s], &map_v, 0, row, &sm.v_full[s]);
-            TRACE(2, v_g)
-            ++v_g;
-            progress = true;
-          }
-        }
-        if (progress) {
-          idle_since = clock64();
-        } else {
-          // nothing to do yet (all cursors run ahead): sleep on the barrier that gates the next S
-          // issue, for at most a microsecond, and leave the issue slots to the softmax warps
-          if (gate) mbar_try_wait_hint(gate, gate_parity, 1000);
-          else __nanosleep(200);
-          if (clock64() - idle_since > kWaitCycles) {
-            *abort_flag = 1;
-            atomicCAS(error_flag, 0, 201);
-          }
+        const int st = k_g % kStagesK;
+        if (!mbar_wait(&sm.k_empty[st], ((k_g / kStagesK) & 1) ^ 1, ab, 212)) break;
+        cp_async_wait<kEntAhead - 1>();  // the copy of entry k_g has landed
+        const int e = *reinterpret_cast<volatile int32_t*>(&sm.ent_stage[k_g % kEntStage]);
+        fetch(k_g + kEntAhead);
+        const int row = ki.kv_row0 + (e >> 2) * 64;
+        const bool last = k_j + 1 == ki.n_entries;
+        sm.ent_ring[k_g % kEntRing] = make_int2(e | (k_j == 0 ? kEntFirst : 0) | (last ? kEntLast : 0), row);
+        __threadfence_block();
+        *reinterpret_cast<volatile uint32_t*>(&sm.k_published) = k_g + 1;
+        mbar_arrive_expect_tx(&sm.k_full[st], kTileBytes);
+        tma_load_2d(sm.k[st], &map_k, 0, row, &sm.k_full[st]);
+        TRACE(1, k_g)
+        ++k_j;
+        if (last) {
+          ++k_item;
+          ++k_itn;
+          k_j = 0;
+          ki = kn;
+          settle_item();
         }
       }
       cp_async_wait<0>();
-      // Leaving on an abort happens only after the pipeline has been idle for the whole
-      // time-out, so none of this thread's copies can still be in flight.
+    }
+  } else if (warp == 6) {
+    // ------------------------------------------------------------------ V loader
+    if (lane == 0) {
+      prefetch_tensormap(&map_v);
+      int ent_first;
+      uint32_t total;
+      cta_entry_range(items, item_begin, item_end, ent_first, total);
+      volatile uint32_t* published = &sm.k_published;
+      volatile int* abort_flag = &sm.abort_flag;
+      bool ok = true;
+      for (uint32_t v_g = 0; ok && v_g < total; ++v_g) {
+        const int st = v_g % kStagesV;
+        if (!mbar_wait(&sm.v_empty[st], ((v_g / kStagesV) & 1) ^ 1, ab, 213)) break;
+        if (*published <= v_g) {  // the record of this entry is not written yet (rare: V runs behind K)
+          const long long t0 = clock64();
+          while (*published <= v_g && !*abort_flag) {
+            __nanosleep(40);
+            if (clock64() - t0 > kWaitCycles) {
+              *abort_flag = 1;
+              atomicCAS(error_flag, 0, 217);
+            }
+          }
+          if (*abort_flag) break;
+        }
+        __threadfence_block();
+        const int row = sm.ent_ring[v_g % kEntRing].y;
+        mbar_arrive_expect_tx(&sm.v_full[st], kTileBytes);
+        tma_load_2d(sm.v[st], &map_v, 0, row, &sm.v_full[st]);
+        TRACE(2, v_g)
+      }
+    }
+  } else if (warp == 7) {
+    // ------------------------------------------------------------------ S = Q K^T issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_f16(128, 64, BF16 ? 1 : 0, false);
+      int ent_first;
+      uint32_t total;
+      cta_entry_range(items, item_begin, item_end, ent_first, total);
+      uint32_t s_itn = 0;
+      for (uint32_t s_g = 0; s_g < total; ++s_g) {
+        const int b = s_g & 1;
+        const int st = s_g % kStagesK;
+        if (!mbar_wait(&sm.k_full[st], (s_g / kStagesK) & 1, ab, 218)) break;
+        // the K loader wrote this entry's record before it armed the barrier just waited for
+        const int rec = *reinterpret_cast<volatile int*>(&sm.ent_ring[s_g % kEntRing].x);
+        const int qb = s_itn & 1;
+        if (rec & kEntFirst) {
+          if (!mbar_wait(&sm.q_full[qb], (s_itn >> 1) & 1, ab, 219)) break;
+        }
+        // buffer b (scores and probabilities) is free once the PV MMA of entry s_g-2 has completed:
+        // the softmax warps finished that entry before its PV MMA was issued
+        if (s_g >= 2) {
+          if (!mbar_wait(&sm.pv_done[b], ((s_g - 2) >> 1) & 1, ab, 220)) break;
+        }
+        tc_fence_after_sync();
+        const uint64_t dq = make_smem_desc_sw128(smem_u32(sm.q[qb]));
+        const uint64_t dk = make_smem_desc_sw128(smem_u32(sm.k[st]));
+        const uint32_t d = tmem_base + kColS + b * 64;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) mma_ss(d, dq + (k * 32 >> 4), dk + (k * 32 >> 4), idesc_s, k ? 1u : 0u);
+        tc_commit(&sm.k_empty[st]);
+        tc_commit(&sm.s_full[b]);
+        TRACE(5, s_g)
+        if (rec & kEntLast) {
+          tc_commit(&sm.q_empty[qb]);
+          ++s_itn;
+        }
+      }
     }
   } else if (warp == 5) {
     // ------------------------------------------------------------------ MMA issuer
@@ -398,7 +422,9 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         if (rec & kEntLast) ++pv_itn;
       }
     }
+  }
   } else {
+    reg_alloc<kRegsSoftmax>();
     // ------------------------------------------------------------------ softmax warps 0..3
     const int row = warp * 32 + lane;  // tile row == TMEM lane
     const int half = row >> 6;         // 0: query block A, 1: query block B
@@ -418,10 +444,12 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         const int b = gj & 1;
         const uint32_t u = gj >> 1;
         TRACE(10, gj)
+        // The S MMA of this entry was issued after the PV MMA of entry gj-2 had completed, so this one
+        // wait also says that the probability buffer b and the score buffer b are free again.
         if (!mbar_wait(&sm.s_full[b], u & 1, ab, 221)) { ok = false; break; }
         TRACE(11, gj)
         tc_fence_after_sync();
-        // the producer published this entry's record before it loaded the K block of the S tile just waited for
+        // the K loader published this entry's record before it loaded the K block of the S tile just waited for
         const bool active = ((sm.ent_ring[gj % kEntRing].x >> half) & 1) != 0;
         uint32_t s[64];
         if (active) {
@@ -429,9 +457,6 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           tmem_ld32(lane_base + kColS + b * 64 + 32, s + 32);
           tc_wait_ld();
         }
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sm.s_free[b]);  // one arrival per warp: 4 instead of 128 updates of the barrier word
         TRACE(12, gj)
         float alpha = 1.f;
         bool fix = false;
@@ -457,11 +482,7 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           }
         }
         // the probability buffer was last read by the PV MMA two entries back
-        if (gj >= 2) {
-          TRACE(13, gj)
-          if (!mbar_wait(&sm.pv_done[b], ((gj - 2) >> 1) & 1, ab, 222)) { ok = false; break; }
-          TRACE(14, gj)
-        }
+
         if (__any_sync(0xffffffffu, fix)) {
           // rescale this warp's rows of the output tile; every PV MMA issued so far must be done
           if (j > 0) {
