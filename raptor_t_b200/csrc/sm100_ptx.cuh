@@ -100,9 +100,7 @@ struct AbortCtx {
 // Bounded wait for the phase with the given parity to complete.  `where` tags the
 // call site in the error word.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const AbortCtx& ab, int where) {
-#ifndef RT_NO_TEST_FIRST
   if (mbar_test_wait(bar, parity)) return true;  // non-blocking test: the cheap path when the phase is already over
-#endif
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (true) {
