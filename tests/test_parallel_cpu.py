@@ -55,3 +55,8 @@ def test_partition_covers_all_sequences_and_balances():
 def test_gather_restores_input_order_gloo_world2():
     lens = [1024, 64, 832, 2048, 1472]
     mp.spawn(_worker, args=(2, _free_port(), lens, 8), nprocs=2, join=True)
+
+
+def test_gather_restores_input_order_gloo_world3_uneven_shares():
+    lens = [4096, 64, 64, 128, 2048, 1472, 704, 64, 3136]
+    mp.spawn(_worker, args=(3, _free_port(), lens, 4), nprocs=3, join=True)
