@@ -149,9 +149,12 @@ rt_status rt_gemm_qkv(void* q_dev, void* k_dev, void* v_dev, const void* a_dev, 
  * tile has 128 rows; its key/value list is the multiset union of the two blocks' lists, each
  * entry tagged with the query blocks that use it.  Opaque handle; holds host + device copies. */
 typedef struct rt_attn_plan rt_attn_plan;
+/* n_ctas <= 0: as many CTAs as the current device keeps resident.  split_entries: key/value lists
+ * longer than this (and than one CTA's share of the batch) are cut into parts whose partial
+ * results a second kernel merges; 0 = never split, < 0 = the library's default. */
 rt_status rt_attn_plan_create(const rt_config* cfg, const int32_t* lens_tokens, int n_seq,
                               const int32_t* kv_ptr_host, const int32_t* kv_idx_host, int n_ctas,
-                              void* stream, rt_attn_plan** plan_out);
+                              int split_entries, void* stream, rt_attn_plan** plan_out);
 rt_status rt_attn_plan_destroy(rt_attn_plan* plan);
 /* issued key/value block loads (work-list entries) and useful visits, for roofline accounting */
 rt_status rt_attn_plan_stats(const rt_attn_plan* plan, int64_t* entries_out, int64_t* visits_out,
@@ -269,6 +272,13 @@ rt_status rt_encoder_plan_stats(rt_encoder* enc, int layer, int64_t* entries_out
                                 int32_t* items_out);
 /* Synchronises the device and reports (then clears) a kernel that gave up on a bounded wait. */
 rt_status rt_check_device(void);
+/* Self-test of that error path: launches one CTA that waits, for at most limit_cycles SM clocks
+ * (1 .. 2e8), on a barrier nothing arrives on.  The kernel then returns normally and leaves wait
+ * site 901 in the error word: target 0 = the per-device word rt_check_device() reads, target 1 =
+ * the status word of rt_sparse_attention_static (reported by that entry point's next call).
+ * Nothing faults or traps; the device stays usable.  The reference has no error reporting at all
+ * (layers/kernels/mat_mul.cpp:50-55 prints and exits), so this has no counterpart there. */
+rt_status rt_selftest_bounded_wait(int64_t limit_cycles, int target, void* stream);
 /* Kernel launches made by this library in this process so far. */
 int64_t rt_kernel_launches(void);
 

@@ -16,7 +16,7 @@ LIB = os.path.join(LIB_DIR, "libraptor_b200.so")
 
 SOURCES = [
     "runtime.cpp", "metadata.cpp", "tma_host.cpp", "elementwise.cu", "gemm_sm100.cu", "gemm_pair_sm100.cu", "attention_sm100.cu",
-    "encoder.cu", "no_alloc.cu",
+    "encoder.cu", "no_alloc.cu", "selftest.cu",
 ]
 
 NVCC_FLAGS = [

@@ -46,6 +46,7 @@ _SIGS = {
     "rt_last_error": (C.c_char_p, []),
     "rt_version": (C.c_int, []),
     "rt_check_device": (C.c_int, []),
+    "rt_selftest_bounded_wait": (C.c_int, [C.c_int64, C.c_int, _vp]),
     "rt_kernel_launches": (C.c_int64, []),
     "rt_rand_block_table": (C.c_int, [C.c_uint32, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _i32p]),
     "rt_count_visits": (C.c_int, [_cfgp, _i32p, C.c_int, _i64p]),
@@ -60,7 +61,7 @@ _SIGS = {
     "rt_gemm": (C.c_int, [_vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp]),
     "rt_gemm_residual": (C.c_int, [_vp, _vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, _vp]),
     "rt_gemm_qkv": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, _vp]),
-    "rt_attn_plan_create": (C.c_int, [_cfgp, _i32p, C.c_int, _i32p, _i32p, C.c_int, _vp, C.POINTER(_vp)]),
+    "rt_attn_plan_create": (C.c_int, [_cfgp, _i32p, C.c_int, _i32p, _i32p, C.c_int, C.c_int, _vp, C.POINTER(_vp)]),
     "rt_attn_plan_destroy": (C.c_int, [_vp]),
     "rt_attn_plan_build_host": (C.c_int, [_cfgp, C.c_uint32, _i32p, C.c_int, C.c_int, C.c_int, _i32p, C.c_int64, _i32p,
                                           C.c_int64, _i32p, _i64p, _i64p, _i64p]),

@@ -47,7 +47,6 @@
 #include <cuda_fp16.h>
 
 #include <algorithm>
-#include <cstdlib>
 #include <vector>
 
 #include "attention.h"
@@ -161,22 +160,6 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
   }
 }
 
-#ifdef RT_ATTN_TRACE
-// Tuning builds only: lane 0 of every warp of CTA 0 logs (clock, event, index) into its own
-// slice with plain stores.
-__device__ unsigned long long g_trace[8 * 1024 * 2];
-#define TRACE_DECL unsigned _tr_i = 0;
-#define TRACE(ev, idx)                                                                      \
-  if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && _tr_i < 1024) {                         \
-    unsigned long long* _p = g_trace + ((threadIdx.x >> 5) * 1024 + _tr_i) * 2;             \
-    _p[0] = clock64();                                                                      \
-    _p[1] = (static_cast<unsigned long long>(ev) << 32) | static_cast<unsigned>(idx);       \
-    ++_tr_i;                                                                                \
-  }
-#else
-#define TRACE_DECL
-#define TRACE(ev, idx)
-#endif
 
 // Register budget: the kernel is launched with 128 registers per thread (two CTAs of 256
 // threads per SM); the four single-thread warps then give registers back and the softmax
@@ -243,7 +226,6 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 
   const int item_begin = cta_ptr[blockIdx.x];
   const int item_end = cta_ptr[blockIdx.x + 1];
-  TRACE_DECL
 
   // Four single-thread roles walk the CTA's flattened (item, entry) stream, each with blocking
   // (bounded) waits on its own barriers, so that their serial latencies (barrier round trips,
@@ -301,7 +283,6 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         *reinterpret_cast<volatile uint32_t*>(&sm.k_published) = k_g + 1;
         mbar_arrive_expect_tx(&sm.k_full[st], kTileBytes);
         tma_load_2d(sm.k[st], &map_k, 0, row, &sm.k_full[st]);
-        TRACE(1, k_g)
         ++k_j;
         if (last) {
           ++k_item;
@@ -341,7 +322,6 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         const int row = sm.ent_ring[v_g % kEntRing].y;
         mbar_arrive_expect_tx(&sm.v_full[st], kTileBytes);
         tma_load_2d(sm.v[st], &map_v, 0, row, &sm.v_full[st]);
-        TRACE(2, v_g)
       }
     }
   } else if (warp == 7) {
@@ -375,7 +355,6 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         for (int k = 0; k < 4; ++k) mma_ss(d, dq + (k * 32 >> 4), dk + (k * 32 >> 4), idesc_s, k ? 1u : 0u);
         tc_commit(&sm.k_empty[st]);
         tc_commit(&sm.s_full[b]);
-        TRACE(5, s_g)
         if (rec & kEntLast) {
           tc_commit(&sm.q_empty[qb]);
           ++s_itn;
@@ -398,9 +377,7 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         const uint32_t u = pv_g >> 1;
         const int st = pv_g % kStagesV;
         const uint32_t ph = (pv_g / kStagesV) & 1;
-        TRACE(6, pv_g)
         if (!mbar_wait(&sm.v_full[st], ph, ab, 214)) { ok = false; break; }
-        TRACE(7, pv_g)
         // the producer wrote this entry's record before it issued the V copy just waited for
         const int rec = *reinterpret_cast<volatile int*>(&sm.ent_ring[pv_g % kEntRing].x);
         const bool first = (rec & kEntFirst) != 0;
@@ -409,7 +386,6 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           if (!mbar_wait(&sm.o_free, (pv_itn & 1) ^ 1, ab, 215)) { ok = false; break; }
         }
         if (!mbar_wait(&sm.p_full[b], u & 1, ab, 216)) { ok = false; break; }
-        TRACE(8, pv_g)
         tc_fence_after_sync();
         const uint64_t dv = make_smem_desc_sw128(smem_u32(sm.v[st]));
         const uint32_t d = tmem_base + kColO;
@@ -418,7 +394,6 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         for (int k = 0; k < 4; ++k) mma_ts(d, a + k * 8, dv + (k * 2048 >> 4), idesc_pv, (!first || k) ? 1u : 0u);
         tc_commit(&sm.v_empty[st]);
         tc_commit(&sm.pv_done[b]);
-        TRACE(9, pv_g)
         if (rec & kEntLast) ++pv_itn;
       }
     }
@@ -443,11 +418,9 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         const uint32_t gj = g + j;
         const int b = gj & 1;
         const uint32_t u = gj >> 1;
-        TRACE(10, gj)
         // The S MMA of this entry was issued after the PV MMA of entry gj-2 had completed, so this one
         // wait also says that the probability buffer b and the score buffer b are free again.
         if (!mbar_wait(&sm.s_full[b], u & 1, ab, 221)) { ok = false; break; }
-        TRACE(11, gj)
         tc_fence_after_sync();
         // the K loader published this entry's record before it loaded the K block of the S tile just waited for
         const bool active = ((sm.ent_ring[gj % kEntRing].x >> half) & 1) != 0;
@@ -457,7 +430,6 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           tmem_ld32(lane_base + kColS + b * 64 + 32, s + 32);
           tc_wait_ld();
         }
-        TRACE(12, gj)
         float alpha = 1.f;
         bool fix = false;
         if (active) {
@@ -530,21 +502,17 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           tmem_st16(lane_base + kColP + b * 32, p);
           tmem_st16(lane_base + kColP + b * 32 + 16, p);
         }
-        TRACE(15, gj)
         tc_wait_st();
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm.p_full[b]);
-        TRACE(16, gj)
       }
       if (!ok) break;
       g += n;
       // final: the last PV MMA of the item completes the output tile
       {
         const uint32_t gl = g - 1;
-        TRACE(17, gl)
         if (!mbar_wait(&sm.pv_done[gl & 1], (gl >> 1) & 1, ab, 224)) { ok = false; break; }
-        TRACE(18, gl)
         tc_fence_after_sync();
       }
       const int tok0 = half == 0 ? item.out_tok0 : item.out_tok1;
@@ -665,27 +633,12 @@ rt_status launch_sparse_attention(void* ctx, const void* q, const void* k, const
   const float scale_log2 = scale * 1.4426950408889634f;
   const int hidden = heads * 64;
   if (dtype == RT_BF16) {
-    static bool set = false;
-    if (!set) {
-      RT_CHECK_CUDA(cudaFuncSetAttribute(sparse_attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         kSmemBytes));
-      // two CTAs per SM need the largest shared-memory carve-out
-      RT_CHECK_CUDA(cudaFuncSetAttribute(sparse_attention_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                         cudaSharedmemCarveoutMaxShared));
-      set = true;
-    }
+    RT_TRY(ensure_kernel_smem(reinterpret_cast<const void*>(sparse_attention_kernel<true>), kSmemBytes, true));
     RT_CHECK_CUDA(launch_kernel(sparse_attention_kernel<true>, dim3(n_ctas), dim3(kThreads), kSmemBytes, st, mq, mk, mv,
                                 (uint16_t*)ctx, items_dev, entries_dev, cta_ptr_dev, hidden, scale_log2, err,
                                 split.part_o, split.part_ml));
   } else {
-    static bool set = false;
-    if (!set) {
-      RT_CHECK_CUDA(cudaFuncSetAttribute(sparse_attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         kSmemBytes));
-      RT_CHECK_CUDA(cudaFuncSetAttribute(sparse_attention_kernel<false>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                         cudaSharedmemCarveoutMaxShared));
-      set = true;
-    }
+    RT_TRY(ensure_kernel_smem(reinterpret_cast<const void*>(sparse_attention_kernel<false>), kSmemBytes, true));
     RT_CHECK_CUDA(launch_kernel(sparse_attention_kernel<false>, dim3(n_ctas), dim3(kThreads), kSmemBytes, st, mq, mk, mv,
                                 (uint16_t*)ctx, items_dev, entries_dev, cta_ptr_dev, hidden, scale_log2, err,
                                 split.part_o, split.part_ml));
@@ -723,7 +676,8 @@ struct rt_attn_plan {
 };
 
 extern "C" rt_status rt_attn_plan_create(const rt_config* cfg, const int32_t* lens, int n_seq, const int32_t* kv_ptr,
-                                         const int32_t* kv_idx, int n_ctas, void* stream, rt_attn_plan** out) {
+                                         const int32_t* kv_idx, int n_ctas, int split_entries, void* stream,
+                                         rt_attn_plan** out) {
   RT_REQUIRE(cfg && lens && kv_ptr && kv_idx && out, RT_ERR_INVALID, "attn_plan_create: null pointer");
   RT_TRY(check_config(cfg));
   RT_TRY(validate_lengths(*cfg, lens, n_seq));
@@ -737,8 +691,7 @@ extern "C" rt_status rt_attn_plan_create(const rt_config* cfg, const int32_t* le
   for (int s = 0; s < n_seq; ++s) nblk += lens[s] / cfg->block;
   const int64_t visits = kv_ptr[nblk];
   auto* p = new rt_attn_plan();
-  int split = kDefaultSplitEntries;
-  if (const char* e = getenv("RAPTOR_B200_ATTN_SPLIT")) split = atoi(e);  // tuning override (0: never split)
+  const int split = split_entries < 0 ? kDefaultSplitEntries : split_entries;
   rt_status s = build_attn_plan(*cfg, lens, n_seq, kv_ptr, kv_idx, visits, n_ctas, p->host, split);
   if (s != RT_OK) {
     delete p;
@@ -806,12 +759,3 @@ extern "C" rt_status rt_sparse_attention(void* ctx, const void* q, const void* k
                                            reinterpret_cast<float*>(plan->dev + plan->part_o_off),
                                            reinterpret_cast<float*>(plan->dev + plan->part_ml_off)});
 }
-
-#ifdef RT_ATTN_TRACE
-extern "C" rt_status rt_attn_trace_read(unsigned long long* out, int reset) {
-  RT_CHECK_CUDA(cudaDeviceSynchronize());
-  RT_CHECK_CUDA(cudaMemcpyFromSymbol(out, rt::g_trace, sizeof(unsigned long long) * 2 * 8 * 1024));
-  if (reset) RT_CHECK_CUDA(cudaMemset([] { void* p; cudaGetSymbolAddress(&p, rt::g_trace); return p; }(), 0, sizeof(unsigned long long) * 2 * 8 * 1024));
-  return RT_OK;
-}
-#endif

@@ -22,6 +22,7 @@
 #include "tma_host.h"
 
 namespace rt {
+int gemm_sm_count();  // gemm_sm100.cu
 namespace {
 
 using namespace ptx;
@@ -177,16 +178,10 @@ rt_status launch_pair(void* c, const void* a, const void* w, const void* bias, i
   RT_TRY(make_tensor_map_2d(&ma, a, M, K, K, 128, kBK, true));
   RT_TRY(make_tensor_map_2d(&mw, w, N, K, K, 128, kBK, true));
   auto kern = gemm_pair_kernel<BF16, EPI>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    RT_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-    attr_set = true;
-  }
+  RT_TRY(ensure_kernel_smem(reinterpret_cast<const void*>(kern), kSmemBytes, false));
   int* err = device_error_word();
   RT_REQUIRE(err != nullptr, RT_ERR_CUDA, "gemm: cannot allocate the device error word");
-  int dev = 0, sms = 148;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int sms = gemm_sm_count();
   const int tiles = ((M + kTileM - 1) / kTileM) * (N / kTileN);
   const int pairs = std::min(tiles, sms / 2);
   RT_CHECK_CUDA(launch_kernel(kern, dim3(2 * pairs), dim3(kThreads), kSmemBytes, st, ma, mw, (uint16_t*)c,

@@ -12,7 +12,7 @@
 #include <cuda_fp16.h>
 
 #include <algorithm>
-#include <cstdlib>
+#include <atomic>
 
 #include "common.h"
 #include "device_error.h"
@@ -23,6 +23,22 @@
 #include "tma_host.h"
 
 namespace rt {
+
+// SM count of the current device (queried once per device).
+int gemm_sm_count() {
+  static std::atomic<int> cache[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  int n = cache[dev].load(std::memory_order_relaxed);
+  if (n == 0) {
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+    cache[dev].store(n, std::memory_order_relaxed);
+  }
+  return n;
+}
+
 namespace {
 
 using namespace ptx;
@@ -171,13 +187,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   }
 }
 
-int gemm_sm_count() {
-  int dev = 0, n = 0;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-  return n > 0 ? n : 148;
-}
-
 template <int BN, bool BF16, int EPI>
 rt_status launch(void* c, const void* a, const void* w, const void* bias, int M, int N, int K, cudaStream_t st,
                  const QkvEpilogue& qkv = QkvEpilogue{}) {
@@ -186,11 +195,7 @@ rt_status launch(void* c, const void* a, const void* w, const void* bias, int M,
   RT_TRY(make_tensor_map_2d(&ma, a, M, K, K, kBM, kBK, true));
   RT_TRY(make_tensor_map_2d(&mw, w, N, K, K, BN, kBK, true));
   auto kern = gemm_kernel<BN, BF16, EPI>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    RT_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-    attr_set = true;
-  }
+  RT_TRY(ensure_kernel_smem(reinterpret_cast<const void*>(kern), Cfg::kSmemBytes, false));
   int* err = device_error_word();
   RT_REQUIRE(err != nullptr, RT_ERR_CUDA, "gemm: cannot allocate the device error word");
   const int tiles = ((M + kBM - 1) / kBM) * (N / BN);
@@ -221,13 +226,7 @@ rt_status gemm_pair_dispatch(void* c, const void* a, const void* w, const void* 
 
 // 256 x 256 CTA-pair tiles pay off when there are enough of them to fill the SM pairs.
 static bool use_pair_tiles(int M, int N) {
-  static const int mode = [] {
-    const char* e = getenv("RAPTOR_B200_GEMM_PAIR");  // 0: never, 1 (default): when the pairs fill the GPU, 2: always
-    return e ? atoi(e) : 1;
-  }();
-  if (mode == 0) return false;
-  if (mode == 2) return N % 256 == 0;  // tuning / tests: whenever the shape allows
-  return N % 256 == 0 && ((M + 255) / 256) * (N / 256) >= 74;
+  return N % 256 == 0 && ((M + 255) / 256) * (N / 256) >= gemm_sm_count() / 2;
 }
 
 }  // namespace rt
@@ -249,15 +248,11 @@ static rt_status gemm_entry(void* c, const void* a, const void* w, const void* b
   if (use_pair_tiles(M, N))
     return gemm_pair_dispatch(c, a, w, bias, M, N, K, epilogue, dtype == RT_BF16, st, extra);
   // largest tile width that divides N and still gives every SM a tile; else the narrowest
-  const int sms = 148;
+  const int sms = gemm_sm_count();
   const int mt = (M + kBM - 1) / kBM;
   int bn = 64;
   if (N % 256 == 0 && mt * (N / 256) >= sms) bn = 256;
   else if (N % 128 == 0 && mt * (N / 128) >= sms) bn = 128;
-  if (const char* f = getenv("RAPTOR_B200_GEMM_BN")) {  // tuning override
-    const int v = atoi(f);
-    if ((v == 64 || v == 128 || v == 256) && N % v == 0) bn = v;
-  }
   const bool bf = dtype == RT_BF16;
   if (bn == 256) return bf ? launch_epi<256, true>(c, a, w, bias, M, N, K, epilogue, st, extra)
                            : launch_epi<256, false>(c, a, w, bias, M, N, K, epilogue, st, extra);
@@ -302,8 +297,9 @@ extern "C" rt_status rt_gemm_qkv(void* q, void* k, void* v, const void* a, const
   if (use_pair_tiles(M, N)) return gemm_pair_dispatch(nullptr, a, w, bias, M, N, K, kEpiQkv, dtype == RT_BF16, st, e);
   const int mt = (M + kBM - 1) / kBM;
   // tile width must divide 3*heads*64 and keep a 32-column chunk inside one head: 64, 128 and 256 all do
-  const bool wide = N % 256 == 0 && mt * (N / 256) >= 148;
-  const bool mid = N % 128 == 0 && mt * (N / 128) >= 148;
+  const int sms = gemm_sm_count();
+  const bool wide = N % 256 == 0 && mt * (N / 256) >= sms;
+  const bool mid = N % 128 == 0 && mt * (N / 128) >= sms;
   const bool bf = dtype == RT_BF16;
   if (wide) return bf ? launch<256, true, kEpiQkv>(nullptr, a, w, bias, M, N, K, st, e)
                       : launch<256, false, kEpiQkv>(nullptr, a, w, bias, M, N, K, st, e);

@@ -4,17 +4,13 @@
 #pragma once
 #include <cuda_runtime.h>
 
-#include <cstdlib>
+#include "common.h"
 
 namespace rt {
 
-inline bool pdl_enabled() {
-  static const bool on = [] {
-    const char* e = getenv("RAPTOR_B200_PDL");
-    return e ? atoi(e) != 0 : true;
-  }();
-  return on;
-}
+// Kernel attributes (dynamic shared-memory limit, carve-out) belong to a (function, device)
+// pair: sets them the first time `func` is launched on the current device.
+rt_status ensure_kernel_smem(const void* func, int smem_bytes, bool max_carveout);
 
 template <typename... KArgs, typename... Args>
 cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
@@ -27,7 +23,7 @@ cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t 
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 

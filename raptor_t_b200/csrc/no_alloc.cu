@@ -22,8 +22,11 @@
 //   * the first call on a device looks up the array's device address
 //     (cudaGetSymbolAddress) and sets the kernel's shared-memory attributes; make
 //     that first call before any stream capture;
-//   * each call starts by reading back the status word of the previous call with a
-//     blocking 4-byte copy, so a kernel that gave up is reported one call late.
+//   * each call starts by reading back the status word of the previous call (a 4-byte
+//     copy queued on the caller's stream, which the host waits for), so a kernel that
+//     gave up is reported one call late - and, because of that wait and of the copies
+//     from temporary host memory, a call on a stream that is being captured is refused
+//     with RT_ERR_UNSUPPORTED.
 #include <cuda_runtime.h>
 
 #include <mutex>
@@ -76,6 +79,15 @@ rt_status scratch_for_current_device(StaticScratch** out, int* sm_count) {
 }
 
 }  // namespace
+
+// The status word of the static scratch on the current device (for the bounded-wait self-test).
+int* static_scratch_status_word() {
+  StaticScratch* sc = nullptr;
+  int sms = 0;
+  if (scratch_for_current_device(&sc, &sms) != RT_OK) return nullptr;
+  return &sc->status;
+}
+
 }  // namespace rt
 
 using namespace rt;
@@ -89,16 +101,25 @@ extern "C" rt_status rt_sparse_attention_static(void* ctx_dev, const void* q_dev
              RT_ERR_INVALID, "sparse_attention_static: null pointer");
   RT_TRY(check_config(cfg));
   RT_TRY(validate_lengths(*cfg, lens_tokens_host, n_seq));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // Every call reads the status word back (the host blocks on it) and copies its work list from
+  // host memory that is released on return: neither can be recorded into a CUDA graph.
+  cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(st, &capturing) != cudaSuccess || capturing != cudaStreamCaptureStatusNone)
+    return fail(RT_ERR_UNSUPPORTED, "sparse_attention_static: the stream is being captured; this entry point "
+                                    "blocks on a status read-back and cannot be recorded into a CUDA graph");
   StaticScratch* sc = nullptr;
   int sms = 0;
   RT_TRY(scratch_for_current_device(&sc, &sms));
   const int n_ctas = 2 * sms;
   RT_REQUIRE(n_ctas <= kMaxCtas, RT_ERR_UNSUPPORTED, "sparse_attention_static: %d SMs exceed the static CTA table", sms);
 
-  // status of the previous call (blocking 4-byte read), then clear it for this one
+  // Status of the previous call, then clear it for this one.  The read is queued on `st` itself, so it
+  // is ordered behind the previous call's kernel whatever kind of stream `st` is (a copy on the legacy
+  // default stream would not wait for a non-blocking stream), and the host waits for it.
   int32_t prev = 0;
-  RT_CHECK_CUDA(cudaMemcpy(&prev, &sc->status, sizeof(prev), cudaMemcpyDeviceToHost));
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  RT_CHECK_CUDA(cudaMemcpyAsync(&prev, &sc->status, sizeof(prev), cudaMemcpyDeviceToHost, st));
+  RT_CHECK_CUDA(cudaStreamSynchronize(st));
   RT_CHECK_CUDA(cudaMemsetAsync(&sc->status, 0, sizeof(int32_t), st));
   if (prev != 0)
     return fail(RT_ERR_DEVICE_WAIT, "sparse_attention_static: the previous call's kernel gave up at wait site %d", prev);

@@ -7,7 +7,11 @@
 #include <mutex>
 #include <vector>
 
+#include <set>
+#include <utility>
+
 #include "device_error.h"
+#include "launch.h"
 #include "launch_count.h"
 #include "metadata.h"
 
@@ -21,6 +25,24 @@ std::string& last_error_ref() {
 std::atomic<int64_t>& launch_counter() {
   static std::atomic<int64_t> c{0};
   return c;
+}
+
+namespace {
+std::mutex g_attr_mu;
+std::set<std::pair<const void*, int>> g_attr_done;  // (kernel, device) pairs whose attributes are set
+}  // namespace
+
+rt_status ensure_kernel_smem(const void* func, int smem_bytes, bool max_carveout) {
+  int dev = 0;
+  RT_CHECK_CUDA(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lk(g_attr_mu);
+  if (g_attr_done.count({func, dev})) return RT_OK;
+  RT_CHECK_CUDA(cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+  if (max_carveout)
+    RT_CHECK_CUDA(cudaFuncSetAttribute(func, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                       cudaSharedmemCarveoutMaxShared));
+  g_attr_done.insert({func, dev});
+  return RT_OK;
 }
 
 namespace {

@@ -93,8 +93,9 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
 
 // Launch-wide error word + CTA-wide abort flag.
 struct AbortCtx {
-  volatile int* cta_flag;   // shared memory
-  int* global_flag;         // global memory, 0 = ok
+  volatile int* cta_flag;          // shared memory
+  int* global_flag;                // global memory, 0 = ok
+  long long limit = kWaitCycles;   // SM clocks after which a wait gives up
 };
 
 // Bounded wait for the phase with the given parity to complete.  `where` tags the
@@ -106,7 +107,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*ab.cta_flag) return false;
-    if (clock64() - t0 > kWaitCycles) break;
+    if (clock64() - t0 > ab.limit) break;
   }
   *ab.cta_flag = 1;
   atomicCAS(ab.global_flag, 0, where);

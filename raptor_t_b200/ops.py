@@ -110,9 +110,10 @@ def gemm_qkv(a, w, bias, block_seq, heads, q_scale=0.125, out=None):
 
 
 class AttentionPlan:
-    """Device work list for rt_sparse_attention built from a CSR block table."""
+    """Device work list for rt_sparse_attention built from a CSR block table.
+    split_entries: lists longer than this are cut into merged parts (0: never, -1: default)."""
 
-    def __init__(self, cfg, lens_tokens, kv_ptr, kv_idx, n_ctas=0):
+    def __init__(self, cfg, lens_tokens, kv_ptr, kv_idx, n_ctas=0, split_entries=-1):
         import numpy as np
         lens = np.ascontiguousarray(lens_tokens, dtype=np.int32)
         kv_ptr = np.ascontiguousarray(kv_ptr, dtype=np.int32)
@@ -120,7 +121,8 @@ class AttentionPlan:
         self._h = C.c_void_p()
         i32p = C.POINTER(C.c_int32)
         check(lib.rt_attn_plan_create(C.byref(cfg), lens.ctypes.data_as(i32p), len(lens), kv_ptr.ctypes.data_as(i32p),
-                                      kv_idx.ctypes.data_as(i32p), n_ctas, _stream(), C.byref(self._h)))
+                                      kv_idx.ctypes.data_as(i32p), n_ctas, int(split_entries), _stream(),
+                                      C.byref(self._h)))
         e, v, it = C.c_int64(), C.c_int64(), C.c_int32()
         check(lib.rt_attn_plan_stats(self._h, C.byref(e), C.byref(v), C.byref(it)))
         self.entries, self.visits, self.items = int(e.value), int(v.value), int(it.value)
@@ -170,3 +172,10 @@ def sparse_attention_static(q, k, v, cfg, lens_tokens, kv_ptr, kv_idx, scale=1.0
 def check_device():
     """Synchronise and raise if any kernel gave up on a bounded device-side wait."""
     check(lib.rt_check_device())
+
+
+def selftest_bounded_wait(limit_cycles=1_000_000, target=0):
+    """Launch the library's self-test kernel whose only wait runs out after `limit_cycles` SM
+    clocks; it returns normally and leaves site 901 in the error word (target 0: the word
+    check_device() reads; 1: the status word of sparse_attention_static)."""
+    check(lib.rt_selftest_bounded_wait(int(limit_cycles), int(target), _stream()))

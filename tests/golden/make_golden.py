@@ -2,7 +2,9 @@
 
 Run once, where the reference checkout is available:
 
-    python tests/golden/make_golden.py /path/to/reference
+    python tests/golden/make_golden.py /path/to/reference [tables small embeddings base config1]
+
+(no group names = all groups)
 
 It imports the reference's validation model (python/modeling_big_bird.py, the
 patched HuggingFace BigBird) as a sub-module of the installed `transformers`
@@ -17,7 +19,11 @@ package, with the one symbol that newer transformers dropped
                  and 20 blocks;
 * hidden_base.npz  - every 16th row of one BigBird-base-shaped layer's output
                  for 13- and 16-block sequences, plus a float64 checksum;
-* embeddings.npz   - embedding output for a tiny vocabulary.
+* embeddings.npz   - embedding output for a tiny vocabulary;
+* hidden_config1.npz - one BigBird-base layer on ONE 4096-token sequence (64 blocks: the
+                 first and last query block attend to all 64 blocks), hidden states ~ N(0, 1),
+                 weights and table seed 0: every 64th row, eight rows of the first and of the
+                 last block, and float64 row sums of all 4096 rows.
 
 The fixtures are inputs to the CPU tests of the oracle (tests/test_oracle.py);
 nothing here is read by the GPU library.
@@ -102,9 +108,24 @@ def ref_table(mbb, seed, heads, L, r, max_pos, block=64):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit(__doc__)
+    ref_root = sys.argv[1]
+    groups = set(sys.argv[2:]) or {"tables", "small", "embeddings", "base", "config1"}
     mbb = load_reference(ref_root)
     from oracle import EncoderConfig, make_weights
+
+    if "config1" in groups:
+        cfg1 = EncoderConfig(layers=1)
+        P1 = make_weights(cfg1, seed=0, nonzero_bias=False, embeddings=False)
+        x = torch.randn(4096, cfg1.hidden, generator=torch.Generator().manual_seed(264))
+        o = run_ref_layers(mbb, cfg1, P1, x, 1)[0]
+        edge = list(range(0, 64, 8)) + list(range(4032, 4096, 8))
+        np.savez_compressed(os.path.join(HERE, "hidden_config1.npz"), rows=o[::64].numpy(), edge_rows=o[edge].numpy(),
+                            edge_index=np.array(edge), row_sums=o.double().sum(dim=1).numpy())
+        print("hidden_config1.npz written")
+    if not groups & {"tables", "small", "embeddings", "base"}:
+        return
 
     # ---- tables ----------------------------------------------------------
     tables = {}

@@ -10,7 +10,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def test_random_batches_are_deterministic_and_split_invariant(monkeypatch):
+def test_random_batches_are_deterministic_and_split_invariant():
     if not torch.cuda.is_available():
         pytest.skip("needs a CUDA device")
     from raptor_t_b200 import capi, metadata, ops
@@ -28,9 +28,8 @@ def test_random_batches_are_deterministic_and_split_invariant(monkeypatch):
         T, H = sum(lens), heads * 64
         g = torch.Generator(device="cuda").manual_seed(int(rng.integers(1 << 30)))
         q, k, v = (torch.randn(T, H, device="cuda", generator=g).to(dtype) for _ in range(3))
-        monkeypatch.setenv("RAPTOR_B200_ATTN_SPLIT", "0")
-        whole = ops.sparse_attention(q, k, v, ops.AttentionPlan(cfg, lens, kv_ptr, kv_idx), scale=0.125)
-        monkeypatch.delenv("RAPTOR_B200_ATTN_SPLIT")
+        whole = ops.sparse_attention(q, k, v, ops.AttentionPlan(cfg, lens, kv_ptr, kv_idx, split_entries=0),
+                                     scale=0.125)
         plan = ops.AttentionPlan(cfg, lens, kv_ptr, kv_idx)
         a = ops.sparse_attention(q, k, v, plan, scale=0.125)
         b = ops.sparse_attention(q, k, v, plan, scale=0.125)

@@ -59,6 +59,21 @@ def test_hidden_states_base_layer(golden_dir):
         assert abs(o.double().abs().sum().item() - s[1]) / s[1] < 1e-6
 
 
+def test_hidden_states_config1_one_base_layer_4096_tokens(golden_dir):
+    """The benchmark's CPU-runnable configuration: one BigBird-base layer, one 4096-token sequence
+    (64 blocks, so the first and last query blocks attend to all 64), seed 0, against rows and
+    row sums recorded from the reference module."""
+    z = np.load(os.path.join(golden_dir, "hidden_config1.npz"))
+    cfg = EncoderConfig(layers=1)
+    P = oracle.make_weights(cfg, seed=0, embeddings=False)
+    x = torch.randn(4096, cfg.hidden, generator=torch.Generator().manual_seed(264))
+    o = oracle.layer_ref(x, P, 0, cfg)
+    assert (o[::64] - torch.from_numpy(z["rows"])).abs().max().item() < 5e-5
+    assert (o[z["edge_index"].tolist()] - torch.from_numpy(z["edge_rows"])).abs().max().item() < 5e-5
+    sums = o.double().sum(dim=1).numpy()
+    assert np.abs(sums - z["row_sums"]).max() < 2e-3  # 768 values of magnitude ~1 per row, fp32 arithmetic
+
+
 def test_embeddings(golden_dir):
     z = np.load(os.path.join(golden_dir, "embeddings.npz"))
     cfg = EncoderConfig(hidden=128, heads=2, ffn=256, layers=2, max_pos=4096, vocab=97)
