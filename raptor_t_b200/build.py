@@ -2,8 +2,10 @@
 
     python -m raptor_t_b200.build [--force]
 
-Output: raptor_t_b200/lib/libraptor_b200.so (git-ignored).  nvcc cross-compiles
-without a GPU, so this also works on a CPU-only build machine.
+Output: raptor_t_b200/lib/libraptor_b200.so - the C-ABI library - and
+raptor_t_b200/lib/raptor_t.so - the pybind11 module `raptor_t` with the reference's operator
+classes on top of it (both git-ignored).  nvcc cross-compiles without a GPU, so this also
+works on a CPU-only build machine.
 """
 import os
 import subprocess
@@ -42,6 +44,35 @@ def _stale():
     return any(os.path.getmtime(d) > t for d in deps if os.path.exists(d))
 
 
+SHIM = os.path.join(LIB_DIR, "raptor_t.so")
+SHIM_SRC = os.path.join(CSRC, "pybind_shim.cpp")
+
+
+def build_shim(force=False):
+    """Compile the pybind11 module `raptor_t` (csrc/pybind_shim.cpp) against torch's headers and
+    link it to libraptor_b200.so; returns its path."""
+    if not force and os.path.exists(SHIM) and os.path.getmtime(SHIM) >= max(
+            os.path.getmtime(SHIM_SRC), os.path.getmtime(LIB),
+            os.path.getmtime(os.path.join(HERE, "..", "include", "raptor_b200.h"))):
+        return SHIM
+    import sysconfig
+
+    import torch
+    tdir = os.path.dirname(torch.__file__)
+    cuda_home = os.path.dirname(os.path.dirname(_nvcc())) if os.path.isabs(_nvcc()) else "/usr/local/cuda"
+    cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", SHIM_SRC, "-o", SHIM, "-DTORCH_EXTENSION_NAME=raptor_t",
+           "-DTORCH_API_INCLUDE_EXTENSION_H", f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
+           f"-I{tdir}/include", f"-I{tdir}/include/torch/csrc/api/include", f"-I{sysconfig.get_paths()['include']}",
+           f"-I{cuda_home}/include", f"-L{tdir}/lib", "-ltorch", "-ltorch_cpu", "-ltorch_python", "-lc10", "-lc10_cuda",
+           "-ltorch_cuda", f"-L{cuda_home}/lib64", "-lcudart", f"-L{LIB_DIR}", "-lraptor_b200", "-Wl,-rpath,$ORIGIN",
+           f"-Wl,-rpath,{tdir}/lib"]
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if r.returncode != 0:
+        sys.stderr.write(r.stdout)
+        raise RuntimeError("raptor_t_b200: building the pybind11 module failed")
+    return SHIM
+
+
 def build(force=False, verbose=False):
     """Compile every CUDA/C++ source into one shared library; returns its path."""
     if not force and not _stale():
@@ -71,3 +102,4 @@ def build(force=False, verbose=False):
 
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_shim(force="--force" in sys.argv))

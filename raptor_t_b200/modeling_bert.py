@@ -89,9 +89,15 @@ class BertModelNoPooler:
 
     @staticmethod
     def from_weights(P, hidden, heads, ffn, layers, dtype=torch.float16, async_=True, eps=1e-12, max_pos=4096,
-                     pattern="bigbird", band_half=4) -> "BertModelNoPooler":
+                     pattern="bigbird", band_half=4, backend=None) -> "BertModelNoPooler":
         """P: dict with HuggingFace BigBird parameter names (torch Linear layout [out, in]); the
-        re-layout to [in, out] + q|k|v concatenation is the reference's (python/modeling_bert.py:138-163)."""
+        re-layout to [in, out] + q|k|v concatenation is the reference's (python/modeling_bert.py:138-163).
+        backend: the operator module - the compiled pybind11 module (raptor_t_b200.compiled.load())
+        or, by default, its ctypes twin raptor_t_b200.raptor_t."""
+        cxx_mod = cxx if backend is None else backend
+        compiled = backend is not None and not hasattr(backend, "LAYER_NORM_EPS")
+        if compiled:
+            backend.set_model_options(num_rand=3, max_pos=max_pos, pattern=pattern, band_half=band_half, eps=eps)
         g = lambda k: P[k].detach().to("cuda", dtype)  # noqa: E731
         emb = BertEmbeddings(P["embeddings.word_embeddings.weight"], P["embeddings.position_embeddings.weight"],
                              P["embeddings.token_type_embeddings.weight"], P["embeddings.LayerNorm.weight"],
@@ -103,14 +109,16 @@ class BertModelNoPooler:
                                g(pre + "attention.self.value.weight")], 0).t().contiguous()
             qkv_b = torch.cat([g(pre + "attention.self.query.bias"), g(pre + "attention.self.key.bias"),
                                g(pre + "attention.self.value.bias")], 0).contiguous()
-            att = cxx.BertAttention(qkv_w, qkv_b, g(pre + "attention.output.dense.weight").t().contiguous(),
-                                    g(pre + "attention.output.dense.bias"), g(pre + "attention.output.LayerNorm.weight"),
-                                    g(pre + "attention.output.LayerNorm.bias"), heads, i, async_, max_pos=max_pos,
-                                    pattern=pattern, band_half=band_half, eps=eps)
-            inter = cxx.BertIntermediate(g(pre + "intermediate.dense.weight").t().contiguous(),
-                                         g(pre + "intermediate.dense.bias"))
-            out = cxx.BertOutput(g(pre + "output.dense.weight").t().contiguous(), g(pre + "output.dense.bias"),
-                                 g(pre + "output.LayerNorm.weight"), g(pre + "output.LayerNorm.bias"), eps)
+            extra = {} if compiled else dict(max_pos=max_pos, pattern=pattern, band_half=band_half, eps=eps)
+            att = cxx_mod.BertAttention(qkv_w, qkv_b, g(pre + "attention.output.dense.weight").t().contiguous(),
+                                        g(pre + "attention.output.dense.bias"),
+                                        g(pre + "attention.output.LayerNorm.weight"),
+                                        g(pre + "attention.output.LayerNorm.bias"), heads, i, async_, **extra)
+            inter = cxx_mod.BertIntermediate(g(pre + "intermediate.dense.weight").t().contiguous(),
+                                             g(pre + "intermediate.dense.bias"))
+            out = cxx_mod.BertOutput(g(pre + "output.dense.weight").t().contiguous(), g(pre + "output.dense.bias"),
+                                     g(pre + "output.LayerNorm.weight"), g(pre + "output.LayerNorm.bias"),
+                                     **({} if compiled else {"eps": eps}))
             ls.append(BertLayer(att, inter, out))
         m = BertModelNoPooler(emb, BertEncoder(ls))
         m.ffn = ffn

@@ -30,8 +30,10 @@ pytestmark = pytest.mark.gpu
 TOL = {
     # name: (max_abs, mean_abs)
     "config2_fp16": (2e-2, 2e-3),
-    "config3_bf16": (1.2e-1, 1.2e-2),
-    "config5_bf16": (2.5e-1, 2.5e-2),
+    # measured on a B200: config 3 max 0.072 / mean 0.0069, config 5 max 0.064 / mean 0.0090 - the fp16
+    # figure (0.0097 / 0.00086) times the 8x coarser mantissa; these bounds are those plus ~50 %
+    "config3_bf16": (1.1e-1, 1.0e-2),
+    "config5_bf16": (1.0e-1, 1.4e-2),
 }
 
 
