@@ -1,43 +1,41 @@
 // Block-sparse attention for sm_100a (tcgen05 + TMEM + TMA), online softmax fused.
 //
-// A persistent CTA walks its list of work items.  An item is up to two 64-token
-// query blocks of one (sequence, head) stacked into a 128-row tile, plus the
-// merged list of 64-token key/value blocks they attend to (global, window and
-// random blocks come from the same table; each entry carries a 2-bit mask that
-// says which of the two query blocks uses it).
+// A persistent CTA walks its list of work items.  An item is up to two 64-token query blocks
+// of one (sequence, head) stacked into a 128-row tile, plus the merged list of 64-token
+// key/value blocks they attend to (global, window and random blocks come from the same
+// table; each entry carries a 2-bit mask that says which of the two query blocks uses it).
+// The list is consumed TWO entries per step: one 128 x 128 score tile, one hand-off.
 //
-// Four warps contribute one thread each, with blocking (bounded) waits on their own
-// barriers, so that their serial latencies run side by side:
-//   warp 4   K / Q loader: TMA loads of the Q tile per item and of one K box (64 x 64,
-//            128-byte swizzle) per list entry into a shared-memory ring.  The only role
-//            that reads the work list in global memory (4-byte asynchronous copies, eight
-//            entries ahead); it publishes one record per entry ({entry, first/last flags,
-//            key/value row}) in a shared-memory ring for the other roles;
-//   warp 6   V loader: one V box per entry into its own ring;
-//   warp 7   issues S = Q K^T (M=128, N=64, K=64; both operands K-major in shared memory)
-//            into one of two TMEM score buffers, as soon as the K block has landed and the
-//            PV MMA two entries back has completed (which frees score buffer and
-//            probability buffer of that parity at once);
-//   warp 5   issues PV = P V (P read from TMEM, V MN-major in shared memory), accumulating
-//            the output tile in TMEM;
-//   warps 0-3  softmax: thread r owns tile row r.  It pulls its score row out of
-//            TMEM, keeps the running max / sum in fp32 (base-2 exponentials) and
-//            writes the 16-bit probabilities back to TMEM for the PV MMA.  The
-//            output tile accumulates in TMEM across the whole list (the PV MMAs
-//            add into it); it is rescaled only when a row's max has grown by more
-//            than 2^8 since the last rescale ("lazy" rescaling: probabilities are
-//            then at most 256, well inside 16-bit range), and read once per item
-//            for the final division by the row sum.  One barrier wait (score tile
-//            ready) and one arrival (probabilities stored) per entry.
-// The kernel is launched with 128 registers per thread; the issue warps hand registers
-// to the softmax warps (setmaxnreg 72 / 184), which hold a 64-column score row each.
+//   warp 4   loader (one thread): TMA loads of the Q tile per item and, per step, of two K
+//            boxes and two V boxes (64 x 64, 128-byte swizzle) into adjacent shared-memory
+//            tiles, so that a step's keys are one 128-row operand and its values one 128-row
+//            operand.  The only role that reads the work list in global memory (4-byte
+//            asynchronous copies, eight entries ahead); it publishes one record per step
+//            ({entries, first/last flags, key/value rows}) in a shared-memory ring.
+//   warp 5   MMA issuer (one thread): S = Q K^T as M=128 N=128 K=64 (both operands K-major in
+//            shared memory) into the score columns of TMEM, and O += P V (P read from TMEM,
+//            V MN-major in shared memory) into the output columns.  The scores of step g+1
+//            are issued as soon as the softmax warps have pulled step g's scores into
+//            registers, i.e. under their exponentials; the PV product of a step is issued in
+//            two halves, each as soon as that half of the probabilities has been stored.
+//   warps 0-3  softmax: thread r owns tile row r (TMEM lane r).  It pulls its score row out of
+//            TMEM, keeps the running max / sum in fp32 (base-2 exponentials) and writes the
+//            16-bit probabilities to their own TMEM columns.  The output tile accumulates in
+//            TMEM across the whole list; it is rescaled only when a row's max has grown by
+//            more than 2^8 since the last rescale ("lazy" rescaling: probabilities are then at
+//            most 256, well inside 16-bit range), and read once per item for the final
+//            division by the row sum.  Warps whose query block does not use an entry skip its
+//            exponentials and keep zeros in its probability columns.
+// The kernel is launched with 128 registers per thread; the upper warpgroup hands registers
+// to the softmax warps (setmaxnreg), which hold a 128-column score row each.
 //
-// Two CTAs share an SM (256 TMEM columns and ~107 KB of shared memory each), so one
-// CTA's softmax latency hides behind the other's.
+// Two CTAs share an SM (256 TMEM columns and ~113 KB of shared memory each): the exponentials
+// (16 per clock per SM) bound the kernel, and one CTA's exponentials run under the other's
+// loads, maxima and stores.
 //
-// Lists that are longer than one CTA's share of the batch are cut into parts by the
-// host; a part leaves its un-normalised fp32 output tile, row maxima and row sums in
-// scratch and merge_partials_kernel combines the parts of a list.
+// Lists that are longer than one CTA's share of the batch are cut into parts by the host; a
+// part leaves its un-normalised fp32 output tile, row maxima and row sums in scratch and
+// merge_partials_kernel combines the parts of a list.
 //
 // Output rows go token-major [T][heads*64].  Counterpart of
 // layers/kernels/sparse_attention.cu:2953-3228; the math follows the reference's
@@ -62,38 +60,38 @@ namespace {
 
 using namespace ptx;
 
-constexpr int kThreads = 256;  // warps 0-3 softmax; 4: K/Q loads, 5: PV issue, 6: V loads, 7: S issue (one thread each)
-constexpr int kStagesK = 4;              // K ring depth (a slot is free again once the S MMA has read it)
-constexpr int kStagesV = 5;              // V ring depth (a slot is held until the PV MMA, two softmax periods later)
-constexpr int kEntRing = 32;             // per-entry records travel from the K cursor to the other roles through smem
+constexpr int kThreads = 256;            // warps 0-3 softmax; 4: loader, 5: MMA issue (one thread each); 6-7 only lend registers
+constexpr int kStagesK = 2;              // K ring depth in steps (a slot is free again once the S MMA has read it)
+constexpr int kStagesV = 3;              // V ring depth in steps (a slot is held until the PV MMA, a softmax period later)
+constexpr int kStepRing = 16;            // per-step records travel from the loader to the other roles through smem
 constexpr int kEntStage = 16;            // landing slots of the asynchronous work-list reads
-constexpr int kEntAhead = 8;             // how many list entries the producer reads ahead
-constexpr int kEntFirst = 1 << 29;       // record flags: first / last entry of its item
-constexpr int kEntLast = 1 << 30;
+constexpr int kEntAhead = 8;             // how many list entries the loader reads ahead
+constexpr int kRecFirst = 1 << 29;       // record flags (in .x): first / last step of its item
+constexpr int kRecLast = 1 << 30;
 constexpr int kTileBytes = 64 * 64 * 2;  // one 64 x 64 16-bit block
-constexpr int kQBytes = 2 * kTileBytes;
+constexpr int kStepBytes = 2 * kTileBytes;
 constexpr int kTmemCols = 256;
-constexpr int kColS = 0;     // 2 x 64 fp32 score columns
-constexpr int kColP = 128;   // 2 x 32 columns of packed 16-bit probabilities
-constexpr int kColO = 192;   // 64 fp32 output columns, accumulated over the item's list
+constexpr int kColS = 0;     // 128 fp32 score columns (two key blocks)
+constexpr int kColO = 128;   // 64 fp32 output columns, accumulated over the item's list
+constexpr int kColP = 192;   // 64 columns of packed 16-bit probabilities (2 x 32)
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 struct Smem {
-  uint8_t q[2][kQBytes];
-  uint8_t k[kStagesK][kTileBytes];
-  uint8_t v[kStagesV][kTileBytes];
+  uint8_t q[2][kStepBytes];
+  uint8_t k[kStagesK][kStepBytes];
+  uint8_t v[kStagesV][kStepBytes];
   uint64_t q_full[2], q_empty[2];
   uint64_t k_full[kStagesK], k_empty[kStagesK], v_full[kStagesV], v_empty[kStagesV];
-  uint64_t s_full[2], p_full[2], pv_done[2], o_free;
-  int2 ent_ring[kEntRing];      // {entry (block << 2 | mask) | flags, row of the key/value block}
+  uint64_t s_full, s_free, p_full[2], pv_done, o_free;
+  int4 step_ring[kStepRing];    // {entry 0 | flags, entry 1 or -1, key/value row of entry 0, of entry 1}
   int32_t ent_stage[kEntStage];
   uint32_t tmem_slot;
   int abort_flag;
-  uint32_t k_published;  // entry records written so far (K loader -> V loader)
 };
 constexpr int kSmemBytes = sizeof(Smem);
+static_assert(kSmemBytes <= 113 * 1024, "two CTAs must fit one SM's shared memory");
 
-// 4-byte asynchronous global -> shared copies: the producer thread reads its work list
+// 4-byte asynchronous global -> shared copies: the loader thread reads its work list
 // ahead without ever stalling on a global load.
 __device__ __forceinline__ void cp_async_4(void* dst_smem, const void* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
@@ -104,18 +102,7 @@ __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-// A CTA's items are consecutive and so are their lists: [first, first + count) of `entries`.
-__device__ __forceinline__ void cta_entry_range(const AttnItem* items, int item_begin, int item_end, int& first,
-                                                uint32_t& count) {
-  first = 0;
-  count = 0;
-  if (item_begin < item_end) {
-    const int a = items[item_begin].entry_off;
-    const AttnItem& z = items[item_end - 1];
-    first = a;
-    count = static_cast<uint32_t>(z.entry_off + z.n_entries - a);
-  }
-}
+__device__ __forceinline__ int steps_of(int n_entries) { return (n_entries + 1) >> 1; }
 
 __device__ __forceinline__ float ex2(float x) {
   float y;
@@ -160,12 +147,48 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
   }
 }
 
+// Row maximum of 64 scores held in registers.
+__device__ __forceinline__ float max64(const uint32_t* s) {
+  float mx0 = __uint_as_float(s[0]), mx1 = __uint_as_float(s[1]);
+  float mx2 = __uint_as_float(s[2]), mx3 = __uint_as_float(s[3]);
+#pragma unroll
+  for (int i = 4; i < 60; i += 8) {
+    mx0 = max3(mx0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+    mx1 = max3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+    mx2 = max3(mx2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
+    mx3 = max3(mx3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
+  }
+  mx0 = max3(mx0, __uint_as_float(s[60]), __uint_as_float(s[61]));
+  mx1 = max3(mx1, __uint_as_float(s[62]), __uint_as_float(s[63]));
+  return fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+}
+
+// p[i] = 2^(s[2i] * c - m), 2^(s[2i+1] * c - m) packed to 16 bits, for 64 scores; returns their sum.
+template <bool BF16>
+__device__ __forceinline__ float exp64(const uint32_t* s, uint32_t* p, float scale_log2, float m_ref) {
+  const unsigned long long c2 = f2_pack(scale_log2, scale_log2);
+  const unsigned long long nm2 = f2_pack(-m_ref, -m_ref);
+  unsigned long long acc0 = 0ull, acc1 = 0ull;  // two packed partial sums (+0.0f, +0.0f)
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const unsigned long long t = f2_fma(f2_pack(__uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1])), c2, nm2);
+    float t0, t1;
+    f2_unpack(t, t0, t1);
+    const float p0 = ex2(t0), p1 = ex2(t1);
+    if (i & 1) acc1 = f2_add(acc1, f2_pack(p0, p1));
+    else acc0 = f2_add(acc0, f2_pack(p0, p1));
+    p[i] = pack2<BF16>(p0, p1);
+  }
+  float s0, s1;
+  f2_unpack(f2_add(acc0, acc1), s0, s1);
+  return s0 + s1;
+}
 
 // Register budget: the kernel is launched with 128 registers per thread (two CTAs of 256
-// threads per SM); the four single-thread warps then give registers back and the softmax
-// warps, which hold a 64-column score row per thread, take them.
-constexpr int kRegsIssue = 72;
-constexpr int kRegsSoftmax = 184;
+// threads per SM); the upper warpgroup then gives registers back and the softmax warps,
+// which hold a 128-column score row per thread, take them.
+constexpr int kRegsIssue = 48;
+constexpr int kRegsSoftmax = 208;
 template <int N>
 __device__ __forceinline__ void reg_dealloc() {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
@@ -196,10 +219,11 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     for (int i = 0; i < 2; ++i) {
       mbar_init(&sm.q_full[i], 1);
       mbar_init(&sm.q_empty[i], 1);
-      mbar_init(&sm.s_full[i], 1);
       mbar_init(&sm.p_full[i], 4);  // one elected arrival per softmax warp
-      mbar_init(&sm.pv_done[i], 1);
     }
+    mbar_init(&sm.s_full, 1);
+    mbar_init(&sm.s_free, 4);
+    mbar_init(&sm.pv_done, 1);
     mbar_init(&sm.o_free, 4);
     for (int s = 0; s < kStagesK; ++s) {
       mbar_init(&sm.k_full[s], 1);
@@ -210,7 +234,6 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       mbar_init(&sm.v_empty[s], 1);
     }
     sm.abort_flag = 0;
-    sm.k_published = 0;
     fence_barrier_init();
   }
   if (warp == 5) {
@@ -227,224 +250,211 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   const int item_begin = cta_ptr[blockIdx.x];
   const int item_end = cta_ptr[blockIdx.x + 1];
 
-  // Four single-thread roles walk the CTA's flattened (item, entry) stream, each with blocking
-  // (bounded) waits on its own barriers, so that their serial latencies (barrier round trips,
-  // descriptor set-up, TMA / MMA issue, commits: several hundred clocks per entry each) run
-  // side by side instead of adding up in one thread.
   if (warp >= 4) {
-  reg_dealloc<kRegsIssue>();  // executed by all four warps of the upper warpgroup at this one place
-  if (warp == 4) {
-    // ------------------------------------------------------------------ K / Q loader
-    // The only role that reads the work list in global memory: entries arrive through 4-byte
-    // asynchronous copies issued kEntAhead entries early, the next item is prefetched in
-    // registers.  It publishes one record per entry for the other roles.
-    if (lane == 0) {
-      prefetch_tensormap(&map_q);
-      prefetch_tensormap(&map_k);
-      int ent_first;
-      uint32_t total;
-      cta_entry_range(items, item_begin, item_end, ent_first, total);
-      const int32_t* ent = entries + ent_first;
-      auto fetch = [&](uint32_t i) {
-        if (i < total) cp_async_4(&sm.ent_stage[i % kEntStage], ent + i);
-        cp_async_commit();  // one group per entry, empty past the end: the wait below counts groups
-      };
-      for (uint32_t i = 0; i < kEntAhead; ++i) fetch(i);
-      int k_item = item_begin, k_j = 0;
-      uint32_t k_itn = 0;
-      AttnItem ki{}, kn{};
-      auto settle_item = [&]() {  // k_item -> first item with a non-empty list; prefetch the one after it
-        while (k_item < item_end && ki.n_entries == 0) {
-          ++k_item;
-          if (k_item < item_end) ki = items[k_item];
+    reg_dealloc<kRegsIssue>();  // executed by all four warps of the upper warpgroup at this one place
+    if (warp == 4) {
+      // ------------------------------------------------------------------ loader
+      // The only role that reads the work list in global memory: entries arrive through 4-byte
+      // asynchronous copies issued kEntAhead entries early, the next item is prefetched in
+      // registers.  A CTA's items are consecutive and so are their lists.
+      if (lane == 0 && item_begin < item_end) {
+        prefetch_tensormap(&map_q);
+        prefetch_tensormap(&map_k);
+        prefetch_tensormap(&map_v);
+        const int ent_first = items[item_begin].entry_off;
+        const AttnItem& zi = items[item_end - 1];
+        const uint32_t total = static_cast<uint32_t>(zi.entry_off + zi.n_entries - ent_first);
+        const int32_t* ent = entries + ent_first;
+        auto fetch = [&](uint32_t i) {
+          if (i < total) cp_async_4(&sm.ent_stage[i % kEntStage], ent + i);
+          cp_async_commit();  // one group per entry, empty past the end: the wait below counts groups
+        };
+        for (uint32_t i = 0; i < kEntAhead; ++i) fetch(i);
+        auto next_entry = [&](uint32_t i) {
+          cp_async_wait<kEntAhead - 1>();  // the copy of entry i has landed
+          const int e = *reinterpret_cast<volatile int32_t*>(&sm.ent_stage[i % kEntStage]);
+          fetch(i + kEntAhead);
+          return e;
+        };
+        uint32_t e_g = 0, step = 0, itn = 0;
+        AttnItem it = items[item_begin];
+        bool ok = true;
+        for (int idx = item_begin; ok && idx < item_end; ++idx) {
+          AttnItem nxt{};
+          if (idx + 1 < item_end) nxt = items[idx + 1];  // in flight while this item's steps are issued
+          const int n = it.n_entries;
+          if (n > 0) {
+            const int qb = itn & 1;
+            if (!mbar_wait(&sm.q_empty[qb], ((itn >> 1) & 1) ^ 1, ab, 211)) break;
+            mbar_arrive_expect_tx(&sm.q_full[qb], kStepBytes);
+            tma_load_2d(sm.q[qb], &map_q, 0, it.q_row0, &sm.q_full[qb]);
+            tma_load_2d(sm.q[qb] + kTileBytes, &map_q, 0, it.q_row1, &sm.q_full[qb]);
+            for (int j = 0; j < n; j += 2, ++step) {
+              const bool two = j + 1 < n;
+              const int sk = step % kStagesK, sv = step % kStagesV;
+              if (!mbar_wait(&sm.k_empty[sk], ((step / kStagesK) & 1) ^ 1, ab, 212)) { ok = false; break; }
+              const int e0 = next_entry(e_g++);
+              const int e1 = two ? next_entry(e_g++) : -1;
+              const int row0 = it.kv_row0 + (e0 >> 2) * 64;
+              const int row1 = two ? it.kv_row0 + (e1 >> 2) * 64 : row0;
+              sm.step_ring[step % kStepRing] =
+                  make_int4(e0 | (j == 0 ? kRecFirst : 0) | (j + 2 >= n ? kRecLast : 0), e1, row0, row1);
+              // the record is written before the barrier is armed: whoever sees the keys arrive sees the record
+              mbar_arrive_expect_tx(&sm.k_full[sk], two ? kStepBytes : kTileBytes);
+              tma_load_2d(sm.k[sk], &map_k, 0, row0, &sm.k_full[sk]);
+              if (two) tma_load_2d(sm.k[sk] + kTileBytes, &map_k, 0, row1, &sm.k_full[sk]);
+              if (!mbar_wait(&sm.v_empty[sv], ((step / kStagesV) & 1) ^ 1, ab, 213)) { ok = false; break; }
+              mbar_arrive_expect_tx(&sm.v_full[sv], two ? kStepBytes : kTileBytes);
+              tma_load_2d(sm.v[sv], &map_v, 0, row0, &sm.v_full[sv]);
+              if (two) tma_load_2d(sm.v[sv] + kTileBytes, &map_v, 0, row1, &sm.v_full[sv]);
+            }
+            ++itn;
+          }
+          it = nxt;
         }
-        if (k_item + 1 < item_end) kn = items[k_item + 1];
-      };
-      if (k_item < item_end) ki = items[k_item];
-      settle_item();
-      bool ok = true;
-      for (uint32_t k_g = 0; ok && k_g < total; ++k_g) {
-        if (k_j == 0) {
-          const int qb = k_itn & 1;
-          if (!mbar_wait(&sm.q_empty[qb], ((k_itn >> 1) & 1) ^ 1, ab, 211)) break;
-          mbar_arrive_expect_tx(&sm.q_full[qb], kQBytes);
-          tma_load_2d(sm.q[qb], &map_q, 0, ki.q_row0, &sm.q_full[qb]);
-          tma_load_2d(sm.q[qb] + kTileBytes, &map_q, 0, ki.q_row1, &sm.q_full[qb]);
-        }
-        const int st = k_g % kStagesK;
-        if (!mbar_wait(&sm.k_empty[st], ((k_g / kStagesK) & 1) ^ 1, ab, 212)) break;
-        cp_async_wait<kEntAhead - 1>();  // the copy of entry k_g has landed
-        const int e = *reinterpret_cast<volatile int32_t*>(&sm.ent_stage[k_g % kEntStage]);
-        fetch(k_g + kEntAhead);
-        const int row = ki.kv_row0 + (e >> 2) * 64;
-        const bool last = k_j + 1 == ki.n_entries;
-        sm.ent_ring[k_g % kEntRing] = make_int2(e | (k_j == 0 ? kEntFirst : 0) | (last ? kEntLast : 0), row);
-        __threadfence_block();
-        *reinterpret_cast<volatile uint32_t*>(&sm.k_published) = k_g + 1;
-        mbar_arrive_expect_tx(&sm.k_full[st], kTileBytes);
-        tma_load_2d(sm.k[st], &map_k, 0, row, &sm.k_full[st]);
-        ++k_j;
-        if (last) {
-          ++k_item;
-          ++k_itn;
-          k_j = 0;
-          ki = kn;
-          settle_item();
-        }
+        cp_async_wait<0>();
       }
-      cp_async_wait<0>();
-    }
-  } else if (warp == 6) {
-    // ------------------------------------------------------------------ V loader
-    if (lane == 0) {
-      prefetch_tensormap(&map_v);
-      int ent_first;
-      uint32_t total;
-      cta_entry_range(items, item_begin, item_end, ent_first, total);
-      volatile uint32_t* published = &sm.k_published;
-      volatile int* abort_flag = &sm.abort_flag;
-      bool ok = true;
-      for (uint32_t v_g = 0; ok && v_g < total; ++v_g) {
-        const int st = v_g % kStagesV;
-        if (!mbar_wait(&sm.v_empty[st], ((v_g / kStagesV) & 1) ^ 1, ab, 213)) break;
-        if (*published <= v_g) {  // the record of this entry is not written yet (rare: V runs behind K)
-          const long long t0 = clock64();
-          while (*published <= v_g && !*abort_flag) {
-            __nanosleep(40);
-            if (clock64() - t0 > kWaitCycles) {
-              *abort_flag = 1;
-              atomicCAS(error_flag, 0, 217);
+    } else if (warp == 5) {
+      // ------------------------------------------------------------------ MMA issuer
+      // The whole warp walks the loop (waits included) and one elected lane issues the MMAs and
+      // commits: loop state and descriptors are then warp-uniform values, which the tensor-core
+      // instructions take directly.  Inside a single-lane branch every descriptor would have to be
+      // moved over from a per-thread register first, and that serial latency (a dozen MMAs per
+      // step) paced the pipeline.
+      if (item_begin < item_end) {
+        const bool leader = elect_one();
+        constexpr uint32_t idesc_s128 = make_idesc_f16(128, 128, BF16 ? 1 : 0, false);
+        constexpr uint32_t idesc_s64 = make_idesc_f16(128, 64, BF16 ? 1 : 0, false);
+        constexpr uint32_t idesc_pv = make_idesc_f16(128, 64, BF16 ? 1 : 0, true);
+        uint32_t total_steps = 0;
+        for (int idx = item_begin; idx < item_end; ++idx) total_steps += steps_of(items[idx].n_entries);
+        uint32_t s_itn = 0, pv_itn = 0;
+        bool ok = true;
+        const uint32_t q_addr = smem_u32(sm.q[0]), k_addr = smem_u32(sm.k[0]), v_addr = smem_u32(sm.v[0]);
+        // S = Q K^T of step g into the score columns (free: the softmax warps hold step g-1's scores in registers)
+        auto issue_s = [&](uint32_t g) -> bool {
+          const int sk = g % kStagesK;
+          if (!mbar_wait(&sm.k_full[sk], (g / kStagesK) & 1, ab, 218)) return false;
+          const int4 rec = sm.step_ring[g % kStepRing];
+          const int qb = s_itn & 1;
+          if (rec.x & kRecFirst) {
+            if (!mbar_wait(&sm.q_full[qb], (s_itn >> 1) & 1, ab, 219)) return false;
+          }
+          tc_fence_after_sync();
+          const uint64_t dq = make_smem_desc_sw128(q_addr + qb * kStepBytes);
+          const uint64_t dk = make_smem_desc_sw128(k_addr + sk * kStepBytes);
+          const uint32_t d = tmem_base + kColS;
+          if (leader) {
+            if (rec.y >= 0) {
+#pragma unroll
+              for (int k = 0; k < 4; ++k) mma_ss(d, dq + (k * 32 >> 4), dk + (k * 32 >> 4), idesc_s128, k ? 1u : 0u);
+            } else {
+#pragma unroll
+              for (int k = 0; k < 4; ++k) mma_ss(d, dq + (k * 32 >> 4), dk + (k * 32 >> 4), idesc_s64, k ? 1u : 0u);
+            }
+            tc_commit(&sm.k_empty[sk]);
+            tc_commit(&sm.s_full);
+            if (rec.x & kRecLast) tc_commit(&sm.q_empty[qb]);
+          }
+          if (rec.x & kRecLast) ++s_itn;
+          __syncwarp();
+          return true;
+        };
+        ok = total_steps == 0 || issue_s(0);
+        for (uint32_t g = 0; ok && g < total_steps; ++g) {
+          const int4 rec = sm.step_ring[g % kStepRing];
+          if (g + 1 < total_steps) {
+            if (!mbar_wait(&sm.s_free, g & 1, ab, 220)) break;  // step g's scores are in registers
+            if (!issue_s(g + 1)) break;
+          }
+          const int sv = g % kStagesV;
+          if (!mbar_wait(&sm.v_full[sv], (g / kStagesV) & 1, ab, 214)) break;
+          const bool first = (rec.x & kRecFirst) != 0;
+          if (first) {
+            // the output tile is overwritten: the softmax warps must have read the previous item's result
+            if (!mbar_wait(&sm.o_free, (pv_itn & 1) ^ 1, ab, 215)) break;
+          }
+          const uint32_t d = tmem_base + kColO;
+          const uint32_t a = tmem_base + kColP;
+          const uint64_t dv = make_smem_desc_sw128(v_addr + sv * kStepBytes);
+          if (!mbar_wait(&sm.p_full[0], g & 1, ab, 216)) break;
+          tc_fence_after_sync();
+          if (leader) {
+            if (first) {
+#pragma unroll
+              for (int k = 0; k < 4; ++k) mma_ts(d, a + k * 8, dv + (k * 2048 >> 4), idesc_pv, k ? 1u : 0u);
+            } else {
+#pragma unroll
+              for (int k = 0; k < 4; ++k) mma_ts(d, a + k * 8, dv + (k * 2048 >> 4), idesc_pv, 1u);
             }
           }
-          if (*abort_flag) break;
-        }
-        __threadfence_block();
-        const int row = sm.ent_ring[v_g % kEntRing].y;
-        mbar_arrive_expect_tx(&sm.v_full[st], kTileBytes);
-        tma_load_2d(sm.v[st], &map_v, 0, row, &sm.v_full[st]);
-      }
-    }
-  } else if (warp == 7) {
-    // ------------------------------------------------------------------ S = Q K^T issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc_f16(128, 64, BF16 ? 1 : 0, false);
-      int ent_first;
-      uint32_t total;
-      cta_entry_range(items, item_begin, item_end, ent_first, total);
-      uint32_t s_itn = 0;
-      for (uint32_t s_g = 0; s_g < total; ++s_g) {
-        const int b = s_g & 1;
-        const int st = s_g % kStagesK;
-        if (!mbar_wait(&sm.k_full[st], (s_g / kStagesK) & 1, ab, 218)) break;
-        // the K loader wrote this entry's record before it armed the barrier just waited for
-        const int rec = *reinterpret_cast<volatile int*>(&sm.ent_ring[s_g % kEntRing].x);
-        const int qb = s_itn & 1;
-        if (rec & kEntFirst) {
-          if (!mbar_wait(&sm.q_full[qb], (s_itn >> 1) & 1, ab, 219)) break;
-        }
-        // buffer b (scores and probabilities) is free once the PV MMA of entry s_g-2 has completed:
-        // the softmax warps finished that entry before its PV MMA was issued
-        if (s_g >= 2) {
-          if (!mbar_wait(&sm.pv_done[b], ((s_g - 2) >> 1) & 1, ab, 220)) break;
-        }
-        tc_fence_after_sync();
-        const uint64_t dq = make_smem_desc_sw128(smem_u32(sm.q[qb]));
-        const uint64_t dk = make_smem_desc_sw128(smem_u32(sm.k[st]));
-        const uint32_t d = tmem_base + kColS + b * 64;
+          if (!mbar_wait(&sm.p_full[1], g & 1, ab, 217)) break;
+          tc_fence_after_sync();
+          if (leader) {
+            if (rec.y >= 0) {  // a single-entry step has nothing in its second half
 #pragma unroll
-        for (int k = 0; k < 4; ++k) mma_ss(d, dq + (k * 32 >> 4), dk + (k * 32 >> 4), idesc_s, k ? 1u : 0u);
-        tc_commit(&sm.k_empty[st]);
-        tc_commit(&sm.s_full[b]);
-        if (rec & kEntLast) {
-          tc_commit(&sm.q_empty[qb]);
-          ++s_itn;
+              for (int k = 0; k < 4; ++k)
+                mma_ts(d, a + 32 + k * 8, dv + ((kTileBytes + k * 2048) >> 4), idesc_pv, 1u);
+            }
+            tc_commit(&sm.v_empty[sv]);
+            tc_commit(&sm.pv_done);
+          }
+          if (rec.x & kRecLast) ++pv_itn;
+          __syncwarp();
         }
       }
     }
-  } else if (warp == 5) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc_pv = make_idesc_f16(128, 64, BF16 ? 1 : 0, true);
-      // this thread issues the PV MMAs; the S MMAs are issued by the producer thread, so the
-      // two serial issue chains (waits, four MMAs, commits per entry) run side by side
-      int ent_first;
-      uint32_t total;
-      cta_entry_range(items, item_begin, item_end, ent_first, total);
-      uint32_t pv_itn = 0;
-      bool ok = true;
-      for (uint32_t pv_g = 0; ok && pv_g < total; ++pv_g) {
-        const int b = pv_g & 1;
-        const uint32_t u = pv_g >> 1;
-        const int st = pv_g % kStagesV;
-        const uint32_t ph = (pv_g / kStagesV) & 1;
-        if (!mbar_wait(&sm.v_full[st], ph, ab, 214)) { ok = false; break; }
-        // the producer wrote this entry's record before it issued the V copy just waited for
-        const int rec = *reinterpret_cast<volatile int*>(&sm.ent_ring[pv_g % kEntRing].x);
-        const bool first = (rec & kEntFirst) != 0;
-        if (first) {
-          // the output tile is overwritten: the softmax warps must have read the previous item's result
-          if (!mbar_wait(&sm.o_free, (pv_itn & 1) ^ 1, ab, 215)) { ok = false; break; }
-        }
-        if (!mbar_wait(&sm.p_full[b], u & 1, ab, 216)) { ok = false; break; }
-        tc_fence_after_sync();
-        const uint64_t dv = make_smem_desc_sw128(smem_u32(sm.v[st]));
-        const uint32_t d = tmem_base + kColO;
-        const uint32_t a = tmem_base + kColP + b * 32;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) mma_ts(d, a + k * 8, dv + (k * 2048 >> 4), idesc_pv, (!first || k) ? 1u : 0u);
-        tc_commit(&sm.v_empty[st]);
-        tc_commit(&sm.pv_done[b]);
-        if (rec & kEntLast) ++pv_itn;
-      }
-    }
-  }
   } else {
     reg_alloc<kRegsSoftmax>();
     // ------------------------------------------------------------------ softmax warps 0..3
     const int row = warp * 32 + lane;  // tile row == TMEM lane
     const int half = row >> 6;         // 0: query block A, 1: query block B
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-    uint32_t g = 0, itn = 0;
+    uint32_t g = 0;
     bool ok = true;
-    AttnItem next_item = item_begin < item_end ? items[item_begin] : AttnItem{};
+    bool pzero0 = false, pzero1 = false;  // this warp's probability columns of half-step 0 / 1 hold zeros
+    // only the fields the softmax warps need: {n_entries, out_tok0, out_tok1, head}
+    auto load_item = [&](int idx) {
+      const int4 hi = reinterpret_cast<const int4*>(items + idx)[1];
+      return hi;
+    };
+    int4 next_item = item_begin < item_end ? load_item(item_begin) : make_int4(0, 0, 0, 0);
     for (int it = item_begin; it < item_end && ok; ++it) {
-      const AttnItem item = next_item;
-      if (it + 1 < item_end) next_item = items[it + 1];  // in flight while this item is processed
-      const int n = item.n_entries;
-      if (n == 0) continue;
+      const int4 item = next_item;
+      if (it + 1 < item_end) next_item = load_item(it + 1);  // in flight while this item is processed
+      const int n_steps = steps_of(item.x);
+      if (n_steps == 0) continue;
       float m_ref = -INFINITY;  // max the stored probabilities / output are relative to (log2 units)
       float l = 0.f;
-      for (int j = 0; j < n; ++j) {
+      for (int j = 0; j < n_steps; ++j) {
         const uint32_t gj = g + j;
-        const int b = gj & 1;
-        const uint32_t u = gj >> 1;
-        // The S MMA of this entry was issued after the PV MMA of entry gj-2 had completed, so this one
-        // wait also says that the probability buffer b and the score buffer b are free again.
-        if (!mbar_wait(&sm.s_full[b], u & 1, ab, 221)) { ok = false; break; }
+        if (!mbar_wait(&sm.s_full, gj & 1, ab, 221)) { ok = false; break; }
         tc_fence_after_sync();
-        // the K loader published this entry's record before it loaded the K block of the S tile just waited for
-        const bool active = ((sm.ent_ring[gj % kEntRing].x >> half) & 1) != 0;
-        uint32_t s[64];
-        if (active) {
-          tmem_ld32(lane_base + kColS + b * 64, s);
-          tmem_ld32(lane_base + kColS + b * 64 + 32, s + 32);
-          tc_wait_ld();
-        }
+        // the loader published this step's record before it loaded the keys of the score tile just waited for
+        const int4 rec = sm.step_ring[gj % kStepRing];
+        const bool two = rec.y >= 0;
+        const bool act0 = ((rec.x >> half) & 1) != 0;
+        const bool act1 = two && ((rec.y >> half) & 1) != 0;
+        // always the whole row: loads under a condition leave the registers "maybe defined", which costs the
+        // register allocator dozens of registers; unused columns are simply ignored
+        uint32_t s[128];
+        tmem_ld32(lane_base + kColS, s);
+        tmem_ld32(lane_base + kColS + 32, s + 32);
+        tmem_ld32(lane_base + kColS + 64, s + 64);
+        tmem_ld32(lane_base + kColS + 96, s + 96);
+        tc_wait_ld();
+        // the score columns may be overwritten by the next step's S MMA
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.s_free);
+
         float alpha = 1.f;
         bool fix = false;
-        if (active) {
-          float mx0 = __uint_as_float(s[0]), mx1 = __uint_as_float(s[1]);
-          float mx2 = __uint_as_float(s[2]), mx3 = __uint_as_float(s[3]);
-#pragma unroll
-          for (int i = 4; i < 60; i += 8) {
-            mx0 = max3(mx0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
-            mx1 = max3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
-            mx2 = max3(mx2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
-            mx3 = max3(mx3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
-          }
-          mx0 = max3(mx0, __uint_as_float(s[60]), __uint_as_float(s[61]));
-          mx1 = max3(mx1, __uint_as_float(s[62]), __uint_as_float(s[63]));
-          const float m_new = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;
+        if (act0 || act1) {
+          float mx = -INFINITY;
+          if (act0) mx = max64(s);
+          if (act1) mx = fmaxf(mx, max64(s + 64));
+          const float m_new = mx * scale_log2;
           if (m_ref == -INFINITY) {
             m_ref = m_new;  // nothing accumulated for this row yet (its output columns are still zero)
           } else if (m_new > m_ref + kRescaleThreshold) {
@@ -453,72 +463,66 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             fix = true;
           }
         }
-        // the probability buffer was last read by the PV MMA two entries back
-
-        if (__any_sync(0xffffffffu, fix)) {
-          // rescale this warp's rows of the output tile; every PV MMA issued so far must be done
-          if (j > 0) {
-            if (!mbar_wait(&sm.pv_done[b ^ 1], ((gj - 1) >> 1) & 1, ab, 223)) { ok = false; break; }
-            tc_fence_after_sync();
-#pragma unroll 1
-            for (int hc = 0; hc < 2; ++hc) {
-              uint32_t o[32];
-              tmem_ld32(lane_base + kColO + hc * 32, o);
-              tc_wait_ld();
-#pragma unroll
-              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-              tmem_st32(lane_base + kColO + hc * 32, o);
-            }
-          }
-          l *= alpha;
+        uint32_t p[32];
+        if (act0) l = l * alpha + exp64<BF16>(s, p, scale_log2, m_ref);
+        else l *= alpha;
+        // the probability columns were last read by the PV MMAs of the previous step; with those complete the
+        // output tile is at rest too
+        if (j > 0) {
+          if (!mbar_wait(&sm.pv_done, (gj - 1) & 1, ab, 223)) { ok = false; break; }
+          tc_fence_after_sync();
         }
-        if (active) {
-          const unsigned long long c2 = f2_pack(scale_log2, scale_log2);
-          const unsigned long long nm2 = f2_pack(-m_ref, -m_ref);
-          unsigned long long acc0 = 0ull, acc1 = 0ull;  // two packed partial sums (+0.0f, +0.0f)
+        if (__any_sync(0xffffffffu, fix) && j > 0) {
+          // rescale this warp's rows of the output tile
+#pragma unroll 1
+          for (int c = 0; c < 64; c += 16) {
+            uint32_t o[16];
+            tmem_ld16(lane_base + kColO + c, o);
+            tc_wait_ld();
 #pragma unroll
-          for (int hc = 0; hc < 2; ++hc) {
-            uint32_t p[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const unsigned long long t =
-                  f2_fma(f2_pack(__uint_as_float(s[32 * hc + 2 * i]), __uint_as_float(s[32 * hc + 2 * i + 1])), c2, nm2);
-              float t0, t1;
-              f2_unpack(t, t0, t1);
-              const float p0 = ex2(t0), p1 = ex2(t1);
-              if (i & 1) acc1 = f2_add(acc1, f2_pack(p0, p1));
-              else acc0 = f2_add(acc0, f2_pack(p0, p1));
-              p[i] = pack2<BF16>(p0, p1);
-            }
-            tmem_st16(lane_base + kColP + b * 32 + hc * 16, p);
+            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st16(lane_base + kColO + c, o);
           }
-          float s0, s1;
-          f2_unpack(f2_add(acc0, acc1), s0, s1);
-          l += s0 + s1;
-        } else {
-          uint32_t p[16];
+        }
+        if (act0) {
+          tmem_st32(lane_base + kColP, p);
+          pzero0 = false;
+        } else if (!pzero0) {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) p[i] = 0u;
-          tmem_st16(lane_base + kColP + b * 32, p);
-          tmem_st16(lane_base + kColP + b * 32 + 16, p);
+          for (int i = 0; i < 32; ++i) p[i] = 0u;
+          tmem_st32(lane_base + kColP, p);
+          pzero0 = true;
         }
         tc_wait_st();
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&sm.p_full[b]);
+        if (lane == 0) mbar_arrive(&sm.p_full[0]);
+        if (two) {
+          if (act1) {
+            l += exp64<BF16>(s + 64, p, scale_log2, m_ref);
+            tmem_st32(lane_base + kColP + 32, p);
+            pzero1 = false;
+          } else if (!pzero1) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) p[i] = 0u;
+            tmem_st32(lane_base + kColP + 32, p);
+            pzero1 = true;
+          }
+          tc_wait_st();
+          tc_fence_before_sync();
+          __syncwarp();
+        }
+        if (lane == 0) mbar_arrive(&sm.p_full[1]);
       }
       if (!ok) break;
-      g += n;
+      g += n_steps;
       // final: the last PV MMA of the item completes the output tile
-      {
-        const uint32_t gl = g - 1;
-        if (!mbar_wait(&sm.pv_done[gl & 1], (gl >> 1) & 1, ab, 224)) { ok = false; break; }
-        tc_fence_after_sync();
-      }
-      const int tok0 = half == 0 ? item.out_tok0 : item.out_tok1;
-      const int slot = (item.head >> 8) - 1;  // >= 0: this item is one part of a split list
+      if (!mbar_wait(&sm.pv_done, (g - 1) & 1, ab, 224)) { ok = false; break; }
+      tc_fence_after_sync();
+      const int tok0 = half == 0 ? item.y : item.z;
+      const int slot = (item.w >> 8) - 1;  // >= 0: this item is one part of a split list
       const float inv = slot >= 0 ? 1.0f : 1.0f / l;
-      uint16_t* dst = ctx + static_cast<size_t>((tok0 >= 0 ? tok0 : 0) + (row & 63)) * hidden + (item.head & 255) * 64;
+      uint16_t* dst = ctx + static_cast<size_t>((tok0 >= 0 ? tok0 : 0) + (row & 63)) * hidden + (item.w & 255) * 64;
       float* pdst = part_o + (static_cast<size_t>(slot >= 0 ? slot : 0) * 128 + row) * 64;
       if (slot >= 0 && tok0 >= 0) {
         float2 ml = make_float2(m_ref, l);
@@ -554,9 +558,7 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           }
         }
       }
-      ++itn;
     }
-    (void)itn;
   }
 
   tc_fence_before_sync();

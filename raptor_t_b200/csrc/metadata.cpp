@@ -316,29 +316,44 @@ void query_block_pairs(const rt_config& cfg, int L, std::vector<std::pair<int, i
 
 // Multiset union of two block lists: an id present in both (per occurrence) gets mask 3,
 // otherwise mask 1 (first list only) or 2 (second list only).  Appends to ent.
+//
+// The kernel consumes a list two entries per step (one 128-column score tile), with the
+// softmax of tile rows 0-63 done by two warps and of rows 64-127 by two others.  The merged
+// list is therefore ordered so that both halves get equal work in every step: shared entries
+// (mask 3) first, then entries of the first and of the second block alternating.
 rt_status merge_lists(const int32_t* la, int na, const int32_t* lb, int nb, int L, std::vector<char>& used,
                       std::vector<int32_t>& ent) {
   for (int i = 0; i < na; ++i)
     RT_REQUIRE(la[i] >= 0 && la[i] < L, RT_ERR_INVALID, "block id %d outside sequence of %d blocks", la[i], L);
   for (int j = 0; j < nb; ++j)
     RT_REQUIRE(lb[j] >= 0 && lb[j] < L, RT_ERR_INVALID, "block id %d outside sequence of %d blocks", lb[j], L);
-  if (na == nb && std::equal(la, la + na, lb)) {
-    for (int i = 0; i < na; ++i) ent.push_back((la[i] << 2) | 3);
+  if (nb == 0 || (na == nb && std::equal(la, la + na, lb))) {
+    for (int i = 0; i < na; ++i) ent.push_back((la[i] << 2) | (nb == 0 ? 1 : 3));
     return RT_OK;
   }
   used.assign(nb, 0);
+  static thread_local std::vector<int32_t> only_a, only_b;
+  only_a.clear();
+  only_b.clear();
   for (int i = 0; i < na; ++i) {
-    int mask = 1;
+    bool both = false;
     for (int j = 0; j < nb; ++j)
       if (!used[j] && lb[j] == la[i]) {
         used[j] = 1;
-        mask = 3;
+        both = true;
         break;
       }
-    ent.push_back((la[i] << 2) | mask);
+    if (both) ent.push_back((la[i] << 2) | 3);
+    else only_a.push_back((la[i] << 2) | 1);
   }
   for (int j = 0; j < nb; ++j)
-    if (!used[j]) ent.push_back((lb[j] << 2) | 2);
+    if (!used[j]) only_b.push_back((lb[j] << 2) | 2);
+  // alternate; when the shared part is odd its last step is completed by the first single-block entry
+  size_t ia = 0, ib = 0;
+  while (ia < only_a.size() || ib < only_b.size()) {
+    if (ia < only_a.size()) ent.push_back(only_a[ia++]);
+    if (ib < only_b.size()) ent.push_back(only_b[ib++]);
+  }
   return RT_OK;
 }
 
@@ -366,14 +381,17 @@ void split_long_items(std::vector<ItemRef>& refs, int split, int n_ctas, AttnPla
       res.push_back(r);
       continue;
     }
-    const int parts = (r.n_entries + split - 1) / split;
-    const int base = r.n_entries / parts, extra = r.n_entries % parts;
+    // parts are whole steps (two entries each); only the last part may end on a single entry
+    const int steps = (r.n_entries + 1) / 2;
+    const int split_steps = std::max(1, split / 2);
+    const int parts = (steps + split_steps - 1) / split_steps;
+    const int base = steps / parts, extra = steps % parts;
     const int32_t g[6] = {out.n_slots, parts, r.it.out_tok0, r.it.out_tok1, r.it.head, 0};
     out.groups.insert(out.groups.end(), g, g + 6);
     int off = 0;
     for (int p = 0; p < parts; ++p) {
       ItemRef part = r;
-      part.n_entries = base + (p < extra ? 1 : 0);
+      part.n_entries = std::min(2 * (base + (p < extra ? 1 : 0)), r.n_entries - off);
       part.ent = r.ent + off;
       part.it.n_entries = part.n_entries;
       part.it.head = r.it.head | ((out.n_slots + 1) << 8);
@@ -386,10 +404,12 @@ void split_long_items(std::vector<ItemRef>& refs, int split, int n_ctas, AttnPla
 }
 
 void assign_and_emit(std::vector<ItemRef>& refs, int n_ctas, AttnPlanHost& out) {
-  // longest-processing-time assignment of items to CTAs (+2: per-item prologue/epilogue cost)
+  // longest-processing-time assignment of items to CTAs; cost = steps of two entries + 1 (per-item
+  // prologue / epilogue)
   std::vector<int> order(refs.size());
   std::iota(order.begin(), order.end(), 0);
-  std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return refs[a].n_entries > refs[b].n_entries; });
+  auto cost_of = [&](int i) { return (refs[i].n_entries + 1) / 2 + 1; };
+  std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return cost_of(a) > cost_of(b); });
   using Entry = std::pair<int64_t, int32_t>;
   std::priority_queue<Entry, std::vector<Entry>, std::greater<Entry>> heap;
   for (int c = 0; c < n_ctas; ++c) heap.emplace(0, c);
@@ -401,7 +421,7 @@ void assign_and_emit(std::vector<ItemRef>& refs, int n_ctas, AttnPlanHost& out) 
     heap.pop();
     cta_of[i] = e.second;
     ++count[e.second + 1];
-    heap.emplace(e.first + refs[i].n_entries + 2, e.second);
+    heap.emplace(e.first + cost_of(i), e.second);
     total_entries += refs[i].n_entries;
   }
   out.cta_ptr.assign(n_ctas + 1, 0);

@@ -28,7 +28,6 @@ package, with the one symbol that newer transformers dropped
 The fixtures are inputs to the CPU tests of the oracle (tests/test_oracle.py);
 nothing here is read by the GPU library.
 """
-import importlib.util
 import os
 import sys
 
@@ -39,35 +38,12 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(HERE, "..", ".."))
 
 
+from oracle.ref_runner import hf_config, ref_layer  # noqa: E402
+from oracle.ref_runner import load_reference as _load_reference  # noqa: E402
+
+
 def load_reference(ref_root):
-    import transformers.pytorch_utils as pu
-    pu.torch_int_div = lambda a, b: torch.div(a, b, rounding_mode="floor")
-    import transformers.models.big_bird  # noqa: F401
-    name = "transformers.models.big_bird.reference_modeling_big_bird"
-    spec = importlib.util.spec_from_file_location(name, os.path.join(ref_root, "python", "modeling_big_bird.py"))
-    mod = importlib.util.module_from_spec(spec)
-    sys.modules[name] = mod
-    spec.loader.exec_module(mod)
-    return mod
-
-
-def hf_config(cfg, attention_type="block_sparse"):
-    from transformers import BigBirdConfig
-    return BigBirdConfig(
-        hidden_size=cfg.hidden, num_attention_heads=cfg.heads, intermediate_size=cfg.ffn,
-        num_hidden_layers=cfg.layers, hidden_act="gelu_new", layer_norm_eps=cfg.eps, block_size=cfg.block,
-        num_random_blocks=cfg.num_rand, max_position_embeddings=cfg.max_pos, attention_type=attention_type,
-        vocab_size=cfg.vocab, type_vocab_size=cfg.type_vocab, hidden_dropout_prob=0.0,
-        attention_probs_dropout_prob=0.0, rescale_embeddings=False, use_bias=True)
-
-
-def ref_layer(mbb, cfg, P, i, attention_type):
-    layer = mbb.BigBirdLayer(hf_config(cfg, attention_type), seed=cfg.seed_of(i)).eval()
-    pre = f"encoder.layer.{i}."
-    sd = {k[len(pre):]: v for k, v in P.items() if k.startswith(pre)}
-    missing, unexpected = layer.load_state_dict(sd, strict=False)
-    assert not unexpected and all("position_ids" in m for m in missing), (missing, unexpected)
-    return layer
+    return _load_reference(os.path.join(ref_root, "python", "modeling_big_bird.py"))
 
 
 @torch.no_grad()
