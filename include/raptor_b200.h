@@ -161,7 +161,9 @@ rt_status rt_attn_plan_stats(const rt_attn_plan* plan, int64_t* entries_out, int
                              int32_t* items_out);
 
 /* The same work list built on the host only (no GPU; for validation and tooling).
- * use_templates = 1 takes the cached per-sequence template path the encoder object uses.
+ * use_templates = 1 takes the cached per-sequence template path the encoder object uses for the
+ * first layer of a batch; 2 its path for the other layers (items, cuts and CTA assignment taken
+ * from another seed's lists, entries refilled from this seed's).
  * items_out: 8 int32 per item {q_row0, q_row1, kv_row0, entry_off, n_entries, out_tok0, out_tok1, head};
  * entries_out: (sequence-local block id << 2) | mask (bit 0: first query block, bit 1: second);
  * cta_ptr_out [n_ctas+1].  Pass items_out = NULL to query the sizes.  No reference counterpart
@@ -170,6 +172,14 @@ rt_status rt_attn_plan_build_host(const rt_config* cfg, uint32_t layer_seed, con
                                   int n_ctas, int use_templates, int32_t* items_out, int64_t items_cap,
                                   int32_t* entries_out, int64_t entries_cap, int32_t* cta_ptr_out,
                                   int64_t* n_items, int64_t* n_entries, int64_t* visits);
+
+/* Upper bounds, valid for every table seed, of the sizes of a batch's work list: work items, list
+ * entries, partial-result slots (one 128 x 64 fp32 tile each) and groups of split lists.  The
+ * encoder object sizes its per-batch metadata regions with these before the tables exist.
+ * split_entries as in rt_attn_plan_create.  No reference counterpart (the reference sizes
+ * to_select_index for one fixed 4096-token sequence, layers/tensor_set.h:61). */
+rt_status rt_attn_plan_bounds(const rt_config* cfg, const int32_t* lens_tokens, int n_seq, int split_entries,
+                              int64_t* items_out, int64_t* entries_out, int64_t* slots_out, int64_t* groups_out);
 
 /* ctx[token][head*64 + d] = softmax(scale * q k_listed^T) v_listed, online softmax, per work item.
  * q/k/v in the head-major layout of rt_qkv_bias_transpose; ctx_dev is token-major [T][heads*64].
@@ -181,15 +191,17 @@ rt_status rt_sparse_attention(void* ctx_dev, const void* q_dev, const void* k_de
  * For callers that may not call cudaMalloc (memory owned by an external arena or caching
  * allocator, a fixed start-up budget, a thread that must not hit an implicit device
  * synchronisation): the work list and the status word live in a file-scope device array of
- * about 0.78 MB that each GPU holds from library load until exit.  Same math and layouts as
+ * about 0.84 MB that each GPU holds from library load until exit.  Same math and layouts as
  * rt_sparse_attention; the block table is given as HOST CSR arrays (rt_build_block_csr).
- * Limits: at most 8192 work items and 131072 list entries per call (about 26 sequences of 4096
- * tokens with 12 heads), else RT_ERR_UNSUPPORTED and nothing runs.  The array is shared by all
+ * Limits: at most 10240 work items and 131072 list entries per call (25 sequences of 4096
+ * tokens with 12 heads fit), else RT_ERR_UNSUPPORTED and nothing runs.  The array is shared by all
  * calls on a device and keeps the last call's contents; calls whose GPU work overlaps race on
  * it, so issue them on one stream.  The first call on a device resolves the array's address
  * and sets kernel attributes: make it before any stream capture.  Each call first reads back
- * (blocking, 4 bytes) and clears the status of the previous call, so a kernel that gave up on a
- * bounded wait is reported by the following call. */
+ * (4 bytes, queued on `stream`; the host waits for it) and clears the status of the previous call,
+ * so a kernel that gave up on a bounded wait is reported by the following call.  Because of that
+ * wait, and because the work list is copied from host memory that is released on return, a call
+ * whose `stream` is being captured is refused with RT_ERR_UNSUPPORTED. */
 rt_status rt_sparse_attention_static(void* ctx_dev, const void* q_dev, const void* k_dev, const void* v_dev,
                                      const rt_config* cfg, const int32_t* lens_tokens_host, int n_seq,
                                      const int32_t* kv_ptr_host, const int32_t* kv_idx_host, float scale,
@@ -258,7 +270,9 @@ rt_status rt_encoder_get_table(rt_encoder* enc, int layer, const int32_t** kv_pt
                                const int32_t** kv_idx_host, int64_t* visits);
 rt_status rt_encoder_get_scratch(rt_encoder* enc, const char* name, void** ptr_dev, size_t* bytes);
 /* device milliseconds of the last forward per stage: "gemm","transpose","attention","layernorm","gelu",
- * "embeddings","pre_process" (host wait for metadata) - the keys of the reference's info dict. */
+ * "embeddings","pre_process" (host wait for metadata) - the keys of the reference's info dict;
+ * "host_blocked": cumulative milliseconds the calling thread has waited for the GPU to release a
+ * metadata slot or a host-pipeline buffer (host time that is not host work). */
 rt_status rt_encoder_get_timing(rt_encoder* enc, const char* key, float* ms_out);
 rt_status rt_encoder_enable_timing(rt_encoder* enc, int on);
 rt_status rt_encoder_kernel_launches(rt_encoder* enc, int64_t* launches_out);

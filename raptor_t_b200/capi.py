@@ -66,6 +66,7 @@ _SIGS = {
     "rt_attn_plan_build_host": (C.c_int, [_cfgp, C.c_uint32, _i32p, C.c_int, C.c_int, C.c_int, _i32p, C.c_int64, _i32p,
                                           C.c_int64, _i32p, _i64p, _i64p, _i64p]),
     "rt_attn_plan_stats": (C.c_int, [_vp, _i64p, _i64p, _i32p]),
+    "rt_attn_plan_bounds": (C.c_int, [_cfgp, _i32p, C.c_int, C.c_int, _i64p, _i64p, _i64p, _i64p]),
     "rt_sparse_attention": (C.c_int, [_vp, _vp, _vp, _vp, _vp, C.c_float, C.c_int, _vp]),
     "rt_sparse_attention_static": (C.c_int, [_vp, _vp, _vp, _vp, _cfgp, _i32p, C.c_int, _i32p, _i32p, C.c_float, C.c_int,
                                              _vp]),

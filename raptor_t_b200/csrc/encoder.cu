@@ -4,12 +4,15 @@
 //
 // Metadata pipeline (rebuild of layers/metadata.cpp + layers/semaphore.cpp +
 // the per-layer std::async workers of layers/multi_headed_attention.h:72-110 on
-// CUDA streams and events): prepare_batch() starts ONE host worker that builds,
-// layer by layer, the block table and the attention work list into pinned memory,
-// enqueues their upload on a side stream and records an event per layer.  The
-// forward pass issues the QKV GEMM and the transpose of layer i first, then makes
-// the compute stream wait on layer i's event (after a host-side check that the
-// event has been recorded), so table construction and upload overlap the GEMMs.
+// CUDA streams and events): the encoder owns ONE persistent host worker.
+// prepare_batch() hands it the batch; it builds, layer by layer, the attention work
+// list into pinned memory, enqueues one upload per layer on a side stream and records
+// an event per layer.  Query-block pairs, cuts of long lists and the assignment of
+// work items to CTAs are computed once per batch (layer 0); the other layers only
+// refill the list entries from their own block tables.  The forward pass issues the
+// QKV GEMM of layer i first, then makes the compute stream wait on layer i's event
+// (after a host-side check that the event has been recorded), so table construction
+// and upload overlap the GEMMs.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -130,8 +133,9 @@ struct rt_encoder {
   int device = 0;
   DevBuf ids_dev, pos_dev;
 
-  // Per-batch metadata lives in one of two slots (batch parity), so the worker can fill
-  // the next batch's tables while the previous batch's kernels still read theirs.
+  // Per-batch metadata lives in one of kSlots slots (round robin), so the worker can fill
+  // the next batches' tables while earlier batches' kernels still read theirs.
+  static constexpr int kSlots = 3;
   // A slot holds, for every layer, one region with the same layout in pinned host
   // memory and on the device: work items | list entries | per-CTA offsets.
   struct Slot {
@@ -144,10 +148,12 @@ struct rt_encoder {
     size_t block_seq_off = 0;          // offset (int32 units) of the per-block table
     cudaEvent_t prefix_ready = nullptr;
     cudaEvent_t forward_done = nullptr;
+    cudaEvent_t uploads_done = nullptr;  // behind the last layer's upload: the pinned region may be rewritten
     bool forward_recorded = false;
+    bool uploads_recorded = false;
     bool used = false;
     std::vector<cudaEvent_t> table_ready;
-  } slots[2];
+  } slots[kSlots];
   uint64_t batch_counter = 0;
   Slot* cur = nullptr;
   size_t region_bytes = 0, items_off = 0, entries_off = 0, cta_off = 0, groups_off = 0;
@@ -175,21 +181,28 @@ struct rt_encoder {
   } jobs[2];
   cudaStream_t pipe_stream = nullptr, copy_stream = nullptr;
   uint64_t next_ticket = 1;
+  // persistent metadata worker: sleeps on `cv` until prepare_batch posts a job
   std::thread worker;
   std::mutex mu;
   std::condition_variable cv;
+  bool job_posted = false, worker_busy = false, worker_exit = false;
   int layers_recorded = 0;
   rt_status worker_status = RT_OK;
   std::string worker_error;
+  PlanSkeleton skeleton;       // of the current batch (layer 0's assembly)
+  AttnPlanHost base_plan;
 
   // timing
   bool timing = false;
   StageTimer timer;
   double pre_process_ms = 0.0;
+  double host_blocked_ms = 0.0;  // cumulative: time the calling thread spent waiting for the GPU to free a slot / buffer
   std::map<std::string, float> last_ms;
 
+  // returns once the worker has finished the batch it was given (it keeps running)
   void join_worker() {
-    if (worker.joinable()) worker.join();
+    std::unique_lock<std::mutex> lk(mu);
+    cv.wait(lk, [&] { return !job_posted && !worker_busy; });
   }
 };
 
@@ -218,17 +231,6 @@ rt_status copy_vec(DevBuf& dst, const void* src, size_t bytes) {
   return RT_OK;
 }
 
-int count_items_per_head(const rt_config& cfg, const std::vector<int32_t>& lens) {
-  int n = 0;
-  for (int len : lens) {
-    const int L = len / cfg.block;
-    if (uses_random_table(cfg, L)) n += 1 + (L - 2 + 1) / 2;
-    else if (cfg.pattern == RT_PATTERN_BAND) n += 1 + (L - 1 + 1) / 2;
-    else n += (L + 1) / 2;
-  }
-  return n;
-}
-
 struct Span {
   rt_encoder* e;
   cudaStream_t st;
@@ -245,12 +247,12 @@ struct Span {
   }
 };
 
-void worker_main(rt_encoder* e) {
-  // One pass over the layers: per-sequence templates (cached across batches) -> batch work
-  // list -> pinned region -> async upload -> event.
-  cudaSetDevice(e->device);
+// One batch: per layer, per-sequence templates (cached across batches) -> work list -> pinned
+// region -> one asynchronous upload -> event.
+void build_batch_metadata(rt_encoder* e) {
   rt_encoder::Slot& slot = *e->cur;
   std::vector<const SeqTemplate*> tmpl(e->n_seq);
+  AttnPlanHost refill;
   for (int l = 0; l < e->cfg.layers; ++l) {
     rt_status s = RT_OK;
     for (int q = 0; q < e->n_seq && s == RT_OK; ++q) {
@@ -266,43 +268,52 @@ void worker_main(rt_encoder* e) {
       }
       if (s == RT_OK) tmpl[q] = &it->second;
     }
-    AttnPlanHost plan;
-    if (s == RT_OK) s = assemble_attn_plan(e->cfg, e->lens.data(), e->n_seq, tmpl.data(), e->attn_ctas, plan);
+    const AttnPlanHost* plan = nullptr;
+    if (s == RT_OK) {
+      if (l == 0) {
+        s = assemble_attn_plan(e->cfg, e->lens.data(), e->n_seq, tmpl.data(), e->attn_ctas, e->base_plan,
+                               kDefaultSplitEntries, &e->skeleton);
+        plan = &e->base_plan;
+      } else {
+        s = refill_attn_plan(e->skeleton, e->base_plan, tmpl.data(), refill);
+        if (s == RT_ERR_STATE)  // a list that is cut changed its length: assemble this layer on its own
+          s = assemble_attn_plan(e->cfg, e->lens.data(), e->n_seq, tmpl.data(), e->attn_ctas, refill);
+        plan = &refill;
+      }
+    }
     if (s == RT_OK) {
       uint8_t* host = slot.meta_pinned + static_cast<size_t>(l) * e->region_bytes;
       uint8_t* dev = static_cast<uint8_t*>(slot.meta_dev.p) + static_cast<size_t>(l) * e->region_bytes;
-      const size_t items_b = plan.items.size() * sizeof(AttnItem);
-      const size_t entries_b = plan.entries.size() * sizeof(int32_t);
-      const size_t cta_b = plan.cta_ptr.size() * sizeof(int32_t);
-      const size_t groups_b = plan.groups.size() * sizeof(int32_t);
+      const size_t items_b = plan->items.size() * sizeof(AttnItem);
+      const size_t entries_b = plan->entries.size() * sizeof(int32_t);
+      const size_t cta_b = plan->cta_ptr.size() * sizeof(int32_t);
+      const size_t groups_b = plan->groups.size() * sizeof(int32_t);
       if (e->items_off + items_b > e->entries_off || e->entries_off + entries_b > e->cta_off ||
           e->cta_off + cta_b > e->groups_off || e->groups_off + groups_b > e->region_bytes ||
-          static_cast<size_t>(plan.n_slots) * 128 * 64 * sizeof(float) > e->part_o.bytes) {
+          static_cast<size_t>(plan->n_slots) * 128 * 64 * sizeof(float) > e->part_o.bytes) {
         s = RT_ERR_STATE;
         last_error_ref() = "metadata region overflow";
       } else {
-        std::memcpy(host + e->items_off, plan.items.data(), items_b);
-        std::memcpy(host + e->entries_off, plan.entries.data(), entries_b);
-        std::memcpy(host + e->cta_off, plan.cta_ptr.data(), cta_b);
-        std::memcpy(host + e->groups_off, plan.groups.data(), groups_b);
-        e->plan_groups[l] = static_cast<int>(plan.groups.size() / 6);
-        cudaError_t ce = cudaMemcpyAsync(dev + e->items_off, host + e->items_off, items_b, cudaMemcpyHostToDevice,
-                                         e->meta_stream);
-        if (ce == cudaSuccess)
-          ce = cudaMemcpyAsync(dev + e->entries_off, host + e->entries_off, entries_b, cudaMemcpyHostToDevice,
-                               e->meta_stream);
-        if (ce == cudaSuccess)
-          ce = cudaMemcpyAsync(dev + e->cta_off, host + e->cta_off, cta_b + (e->groups_off - e->cta_off - cta_b) + groups_b,
-                               cudaMemcpyHostToDevice, e->meta_stream);  // per-CTA offsets and the groups behind them
+        std::memcpy(host + e->items_off, plan->items.data(), items_b);
+        std::memcpy(host + e->entries_off, plan->entries.data(), entries_b);
+        std::memcpy(host + e->cta_off, plan->cta_ptr.data(), cta_b);
+        std::memcpy(host + e->groups_off, plan->groups.data(), groups_b);
+        e->plan_groups[l] = static_cast<int>(plan->groups.size() / 6);
+        // one copy for the whole region of the layer (items | entries | per-CTA offsets | groups)
+        cudaError_t ce = cudaMemcpyAsync(dev, host, e->groups_off + groups_b, cudaMemcpyHostToDevice, e->meta_stream);
         if (ce == cudaSuccess) ce = cudaEventRecord(slot.table_ready[l], e->meta_stream);
+        if (ce == cudaSuccess && l + 1 == e->cfg.layers) {
+          ce = cudaEventRecord(slot.uploads_done, e->meta_stream);
+          slot.uploads_recorded = ce == cudaSuccess;
+        }
         if (ce != cudaSuccess) {
           s = RT_ERR_CUDA;
           last_error_ref() = cudaGetErrorString(ce);
         }
-        e->plan_entries[l] = static_cast<int64_t>(plan.entries.size());
+        e->plan_entries[l] = static_cast<int64_t>(plan->entries.size());
         if (l == 0) {
-          e->plan_visits = plan.visits;
-          e->plan_items = static_cast<int>(plan.items.size());
+          e->plan_visits = plan->visits;
+          e->plan_items = static_cast<int>(plan->items.size());
         }
       }
     }
@@ -318,6 +329,22 @@ void worker_main(rt_encoder* e) {
     }
     e->cv.notify_all();
     if (s != RT_OK) return;
+  }
+}
+
+void worker_main(rt_encoder* e) {
+  cudaSetDevice(e->device);
+  std::unique_lock<std::mutex> lk(e->mu);
+  while (true) {
+    e->cv.wait(lk, [&] { return e->job_posted || e->worker_exit; });
+    if (e->worker_exit) return;
+    e->job_posted = false;
+    e->worker_busy = true;
+    lk.unlock();
+    build_batch_metadata(e);
+    lk.lock();
+    e->worker_busy = false;
+    e->cv.notify_all();
   }
 }
 
@@ -447,6 +474,28 @@ rt_status run_output(rt_encoder* e, int l, const void* ffn, const void* residual
   return RT_OK;
 }
 
+// varlen offsets [n_seq+1] and, behind them, {first token of its sequence, sequence length} of every packed
+// block (the fused QKV epilogue's map), written to the slot's pinned buffer and uploaded
+rt_status fill_prefix_impl(rt_encoder* e, rt_encoder::Slot& slot, const int32_t* lens, int n_seq, int prefix_ints,
+                           int need_ints) {
+  RT_TRY(rt_seq_block_prefix(lens, n_seq, e->cfg.block, slot.prefix_pinned));
+  slot.block_seq_off = prefix_ints;
+  int32_t* bs = slot.prefix_pinned + prefix_ints;
+  int t0 = 0, b = 0;
+  for (int q = 0; q < n_seq; ++q) {
+    for (int i = 0; i < lens[q] / e->cfg.block; ++i, ++b) {
+      bs[2 * b] = t0;
+      bs[2 * b + 1] = lens[q];
+    }
+    t0 += lens[q];
+  }
+  RT_CHECK_CUDA(cudaMemcpyAsync(slot.prefix_dev.p, slot.prefix_pinned, need_ints * sizeof(int32_t),
+                                cudaMemcpyHostToDevice, e->meta_stream));
+  RT_CHECK_CUDA(cudaEventRecord(slot.prefix_ready, e->meta_stream));
+  return RT_OK;
+}
+#define fill_prefix(e, slot, lens, n_seq, a, b) RT_TRY(fill_prefix_impl(e, slot, lens, n_seq, a, b))
+
 }  // namespace
 
 extern "C" rt_status rt_encoder_create(const rt_config* cfg, rt_encoder** out) {
@@ -477,9 +526,11 @@ extern "C" rt_status rt_encoder_create(const rt_config* cfg, rt_encoder** out) {
   for (auto& slot : e->slots) {
     cudaEventCreateWithFlags(&slot.prefix_ready, cudaEventDisableTiming);
     cudaEventCreateWithFlags(&slot.forward_done, cudaEventDisableTiming);
+    cudaEventCreateWithFlags(&slot.uploads_done, cudaEventDisableTiming);
     slot.table_ready.resize(cfg->layers);
     for (auto& ev : slot.table_ready) cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
   }
+  e->worker = std::thread(worker_main, e);
   *out = e;
   return RT_OK;
 }
@@ -487,6 +538,12 @@ extern "C" rt_status rt_encoder_create(const rt_config* cfg, rt_encoder** out) {
 extern "C" rt_status rt_encoder_destroy(rt_encoder* e) {
   if (!e) return RT_OK;
   e->join_worker();
+  {
+    std::lock_guard<std::mutex> lk(e->mu);
+    e->worker_exit = true;
+  }
+  e->cv.notify_all();
+  if (e->worker.joinable()) e->worker.join();
   cudaDeviceSynchronize();
   for (auto& l : e->layers)
     for (DevBuf* b : {&l.qkv_w, &l.qkv_b, &l.ao_w, &l.ao_b, &l.aln_g, &l.aln_b, &l.up_w, &l.up_b, &l.down_w, &l.down_b,
@@ -503,6 +560,7 @@ extern "C" rt_status rt_encoder_destroy(rt_encoder* e) {
     if (slot.prefix_pinned) cudaFreeHost(slot.prefix_pinned);
     cudaEventDestroy(slot.prefix_ready);
     cudaEventDestroy(slot.forward_done);
+    cudaEventDestroy(slot.uploads_done);
     for (auto& ev : slot.table_ready) cudaEventDestroy(ev);
   }
   for (auto& ev : e->timer.pool) cudaEventDestroy(ev);
@@ -594,55 +652,30 @@ extern "C" rt_status rt_encoder_prepare_batch(rt_encoder* e, const int32_t* lens
   RT_TRY(ensure_scratch(e, T));
 
   // this batch's slot; its previous user (two batches ago) must have finished on the device
-  rt_encoder::Slot& slot = e->slots[e->batch_counter & 1];
+  rt_encoder::Slot& slot = e->slots[e->batch_counter % rt_encoder::kSlots];
   ++e->batch_counter;
+  const auto blocked_t0 = std::chrono::steady_clock::now();
   if (slot.forward_recorded) RT_CHECK_CUDA(cudaEventSynchronize(slot.forward_done));
   else if (slot.used) RT_CHECK_CUDA(cudaDeviceSynchronize());  // driven through the per-operator calls
+  // this slot's earlier uploads read the pinned memory that is about to be rewritten
+  if (slot.uploads_recorded) RT_CHECK_CUDA(cudaEventSynchronize(slot.uploads_done));
+  else if (slot.used) RT_CHECK_CUDA(cudaStreamSynchronize(e->meta_stream));
+  e->host_blocked_ms += std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - blocked_t0).count();
   slot.used = true;
-  RT_CHECK_CUDA(cudaStreamSynchronize(e->meta_stream));  // earlier uploads read pinned memory we are about to reuse
   slot.forward_recorded = false;
+  slot.uploads_recorded = false;
   e->cur = &slot;
 
   // varlen offsets + per-block {first token of the sequence, sequence length}
   const int prefix_ints = ((n_seq + 1 + 7) / 8) * 8;  // keeps the block table 32-byte aligned
   const int need_ints = prefix_ints + 2 * e->n_blocks;
-  if (need_ints > slot.prefix_cap) {
-    if (slot.prefix_pinned) cudaFreeHost(slot.prefix_pinned);
-    slot.prefix_pinned = nullptr;
-    slot.prefix_cap = std::max(2 * need_ints, 1024);
-    RT_CHECK_CUDA(cudaMallocHost(&slot.prefix_pinned, slot.prefix_cap * sizeof(int32_t)));
-    RT_TRY(slot.prefix_dev.ensure(slot.prefix_cap * sizeof(int32_t)));
-  }
-  RT_TRY(rt_seq_block_prefix(lens, n_seq, e->cfg.block, slot.prefix_pinned));
-  slot.block_seq_off = prefix_ints;
-  {
-    int32_t* bs = slot.prefix_pinned + prefix_ints;
-    int t0 = 0, b = 0;
-    for (int q = 0; q < n_seq; ++q) {
-      for (int i = 0; i < lens[q] / e->cfg.block; ++i, ++b) {
-        bs[2 * b] = t0;
-        bs[2 * b + 1] = lens[q];
-      }
-      t0 += lens[q];
-    }
-  }
-  RT_CHECK_CUDA(cudaMemcpyAsync(slot.prefix_dev.p, slot.prefix_pinned, need_ints * sizeof(int32_t),
-                                cudaMemcpyHostToDevice, e->meta_stream));
-  RT_CHECK_CUDA(cudaEventRecord(slot.prefix_ready, e->meta_stream));
 
-  // per-layer regions
-  int64_t visits = 0;
-  RT_TRY(rt_count_visits(&e->cfg, lens, n_seq, &visits));
-  // split lists: at most one group per (sequence, head); every part is one more item and one scratch slot
-  size_t slots_bound = 0;
-  for (int q = 0; q < n_seq; ++q)
-    slots_bound += static_cast<size_t>(lens[q] / e->cfg.block + kDefaultSplitEntries - 1) / kDefaultSplitEntries + 1;
-  slots_bound *= e->cfg.heads;
-  const size_t groups_bound = static_cast<size_t>(n_seq) * e->cfg.heads;
-  const size_t n_items = static_cast<size_t>(count_items_per_head(e->cfg, e->lens)) * e->cfg.heads + slots_bound;
+  // per-layer regions, sized by bounds that hold for every table seed
+  size_t n_items = 0, n_entries = 0, slots_bound = 0, groups_bound = 0;
+  attn_plan_bounds(e->cfg, lens, n_seq, kDefaultSplitEntries, &n_items, &n_entries, &slots_bound, &groups_bound);
   e->items_off = 0;
   e->entries_off = align256(n_items * sizeof(AttnItem));
-  e->cta_off = e->entries_off + align256(static_cast<size_t>(visits) * e->cfg.heads * sizeof(int32_t));
+  e->cta_off = e->entries_off + align256(n_entries * sizeof(int32_t));
   e->groups_off = e->cta_off + align256((e->attn_ctas + 1) * sizeof(int32_t));
   e->region_bytes = e->groups_off + align256(groups_bound * 6 * sizeof(int32_t));
   if (slots_bound * 128 * 64 * sizeof(float) > e->part_o.bytes) {
@@ -650,24 +683,43 @@ extern "C" rt_status rt_encoder_prepare_batch(rt_encoder* e, const int32_t* lens
     RT_TRY(e->part_o.ensure(slots_bound * 128 * 64 * sizeof(float)));
     RT_TRY(e->part_ml.ensure(slots_bound * 128 * 2 * sizeof(float)));
   }
+  // Metadata buffers of ALL slots grow together, at the first batch that needs more: a serving loop
+  // that has seen its largest batch once never allocates again, whichever slot a batch lands in.
   const size_t need = e->region_bytes * e->cfg.layers;
-  if (need > slot.meta_cap) {
-    if (slot.meta_pinned) cudaFreeHost(slot.meta_pinned);
-    slot.meta_pinned = nullptr;
-    slot.meta_cap = 0;
-    RT_CHECK_CUDA(cudaMallocHost(&slot.meta_pinned, need + need / 4));
-    RT_TRY(slot.meta_dev.ensure(need + need / 4));
-    slot.meta_cap = need + need / 4;
+  if (need > slot.meta_cap || need_ints > slot.prefix_cap) {
+    RT_CHECK_CUDA(cudaDeviceSynchronize());  // the other slots may still be read by queued kernels and uploads
+    const size_t meta_cap = std::max(slot.meta_cap, need + need / 4);
+    const int prefix_cap = std::max(slot.prefix_cap, std::max(2 * need_ints, 1024));
+    for (auto& sl : e->slots) {
+      if (sl.meta_cap < meta_cap) {
+        if (sl.meta_pinned) cudaFreeHost(sl.meta_pinned);
+        sl.meta_pinned = nullptr;
+        sl.meta_cap = 0;
+        RT_CHECK_CUDA(cudaMallocHost(&sl.meta_pinned, meta_cap));
+        RT_TRY(sl.meta_dev.ensure(meta_cap));
+        sl.meta_cap = meta_cap;
+      }
+      if (sl.prefix_cap < prefix_cap) {
+        if (sl.prefix_pinned) cudaFreeHost(sl.prefix_pinned);
+        sl.prefix_pinned = nullptr;
+        sl.prefix_cap = 0;
+        RT_CHECK_CUDA(cudaMallocHost(&sl.prefix_pinned, prefix_cap * sizeof(int32_t)));
+        RT_TRY(sl.prefix_dev.ensure(prefix_cap * sizeof(int32_t)));
+        sl.prefix_cap = prefix_cap;
+      }
+    }
   }
+  fill_prefix(e, slot, lens, n_seq, prefix_ints, need_ints);
+  e->pre_process_ms = 0.0;
+  e->csr_valid.assign(e->cfg.layers, false);
   {
     std::lock_guard<std::mutex> lk(e->mu);
     e->layers_recorded = 0;
     e->worker_status = RT_OK;
     e->worker_error.clear();
+    e->job_posted = true;
   }
-  e->pre_process_ms = 0.0;
-  e->csr_valid.assign(e->cfg.layers, false);
-  e->worker = std::thread(worker_main, e);
+  e->cv.notify_all();
   e->prepared = true;
   return RT_OK;
 }
@@ -769,7 +821,9 @@ extern "C" rt_status rt_encoder_submit_host(rt_encoder* e, const int32_t* lens, 
   }
   rt_encoder::HostJob& job = e->jobs[e->next_ticket & 1];
   if (job.busy) {  // at most two batches in flight: this buffer's previous batch must have reached the host
+    const auto t0 = std::chrono::steady_clock::now();
     RT_CHECK_CUDA(cudaEventSynchronize(job.copied));
+    e->host_blocked_ms += std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
     job.busy = false;
   }
   // a forward issued through the device-buffer entry points on another stream shares the scratch
@@ -864,6 +918,10 @@ extern "C" rt_status rt_encoder_get_timing(rt_encoder* e, const char* key, float
   RT_REQUIRE(e && key && ms_out, RT_ERR_INVALID, "get_timing: null pointer");
   if (std::strcmp(key, "pre_process") == 0) {
     *ms_out = static_cast<float>(e->pre_process_ms);
+    return RT_OK;
+  }
+  if (std::strcmp(key, "host_blocked") == 0) {  // cumulative since the encoder was created
+    *ms_out = static_cast<float>(e->host_blocked_ms);
     return RT_OK;
   }
   RT_CHECK_CUDA(cudaDeviceSynchronize());

@@ -361,6 +361,10 @@ struct ItemRef {
   int32_t n_entries;
   const int32_t* ent;
   AttnItem it;
+  int32_t seq = -1;      // source of the list for PlanSkeleton: sequence, item index inside its template,
+  int32_t tmpl_item = 0; // offset of this part inside the template item's list, and whether it is a part
+  int32_t part_off = 0;
+  int32_t is_part = 0;
 };
 
 // Cuts long lists into near-equal parts; each part becomes an item of its own that writes a
@@ -395,6 +399,8 @@ void split_long_items(std::vector<ItemRef>& refs, int split, int n_ctas, AttnPla
       part.ent = r.ent + off;
       part.it.n_entries = part.n_entries;
       part.it.head = r.it.head | ((out.n_slots + 1) << 8);
+      part.part_off = off;
+      part.is_part = 1;
       off += part.n_entries;
       ++out.n_slots;
       res.push_back(part);
@@ -403,7 +409,7 @@ void split_long_items(std::vector<ItemRef>& refs, int split, int n_ctas, AttnPla
   refs.swap(res);
 }
 
-void assign_and_emit(std::vector<ItemRef>& refs, int n_ctas, AttnPlanHost& out) {
+void assign_and_emit(std::vector<ItemRef>& refs, int n_ctas, AttnPlanHost& out, PlanSkeleton* skel = nullptr) {
   // longest-processing-time assignment of items to CTAs; cost = steps of two entries + 1 (per-item
   // prologue / epilogue)
   std::vector<int> order(refs.size());
@@ -442,6 +448,13 @@ void assign_and_emit(std::vector<ItemRef>& refs, int n_ctas, AttnPlanHost& out) 
     std::copy(r.ent, r.ent + r.n_entries, out.entries.begin() + off);
     off += r.n_entries;
     out.items[sidx] = it;
+  }
+  if (skel) {
+    skel->src.resize(refs.size());
+    for (size_t sidx = 0; sidx < refs.size(); ++sidx) {
+      const ItemRef& r = refs[pos_item[sidx]];
+      skel->src[sidx] = PlanSkeleton::Src{r.seq, r.tmpl_item, r.part_off, r.is_part ? r.n_entries : -1};
+    }
   }
 }
 
@@ -549,7 +562,7 @@ rt_status build_seq_template(const rt_config& cfg, uint32_t seed, int L, TableCa
 
 rt_status assemble_attn_plan(const rt_config& cfg, const int32_t* lens, int n_seq,
                              const SeqTemplate* const* templates, int n_ctas, AttnPlanHost& out,
-                             int split_entries) {
+                             int split_entries, PlanSkeleton* skel) {
   RT_REQUIRE(n_ctas > 0, RT_ERR_INVALID, "attention plan needs at least one CTA");
   const int nh = cfg.heads, B = cfg.block;
   out = AttnPlanHost();
@@ -576,6 +589,8 @@ rt_status assemble_attn_plan(const rt_config& cfg, const int32_t* lens, int n_se
         r.it.head = h;
         r.it.entry_off = 0;
         r.it.n_entries = r.n_entries;
+        r.seq = s;
+        r.tmpl_item = idx;
         refs.push_back(r);
       }
     }
@@ -583,10 +598,78 @@ rt_status assemble_attn_plan(const rt_config& cfg, const int32_t* lens, int n_se
     tok0 += lens[s];
   }
   split_long_items(refs, split_entries, n_ctas, out);
-  assign_and_emit(refs, n_ctas, out);
+  assign_and_emit(refs, n_ctas, out, skel);
   out.total_tokens = tok0;
   out.heads = nh;
   return RT_OK;
+}
+
+rt_status refill_attn_plan(const PlanSkeleton& skel, const AttnPlanHost& base, const SeqTemplate* const* templates,
+                           AttnPlanHost& out) {
+  RT_REQUIRE(skel.src.size() == base.items.size(), RT_ERR_STATE, "plan skeleton does not match its plan");
+  out.items = base.items;
+  out.cta_ptr = base.cta_ptr;
+  out.groups = base.groups;
+  out.n_slots = base.n_slots;
+  out.total_tokens = base.total_tokens;
+  out.heads = base.heads;
+  out.visits = base.visits;
+  out.entries.clear();
+  out.entries.reserve(base.entries.size() + base.entries.size() / 8);
+  for (size_t i = 0; i < skel.src.size(); ++i) {
+    const PlanSkeleton::Src& sr = skel.src[i];
+    const SeqTemplate& t = *templates[sr.seq];
+    RT_REQUIRE(sr.tmpl_item + 1 < static_cast<int>(t.item_off.size()), RT_ERR_STATE, "template does not fit the skeleton");
+    const int32_t* list = t.ent.data() + t.item_off[sr.tmpl_item];
+    const int full = t.item_off[sr.tmpl_item + 1] - t.item_off[sr.tmpl_item];
+    int n = full;
+    if (sr.part_len >= 0) {  // one part of a split list: the same cut in every layer
+      RT_REQUIRE(sr.part_off + sr.part_len <= full, RT_ERR_STATE, "split list changed its length between layers");
+      list += sr.part_off;
+      n = sr.part_len;
+    }
+    AttnItem& it = out.items[i];
+    it.entry_off = static_cast<int32_t>(out.entries.size());
+    it.n_entries = n;
+    out.entries.insert(out.entries.end(), list, list + n);
+  }
+  return RT_OK;
+}
+
+void attn_plan_bounds(const rt_config& cfg, const int32_t* lens, int n_seq, int split_entries, size_t* items,
+                      size_t* entries, size_t* slots, size_t* groups) {
+  size_t n_items = 0, n_entries = 0, n_slots = 0, n_groups = 0;
+  std::vector<std::pair<int, int>> pairs;
+  const int split = split_entries > 0 ? split_entries : 0;
+  for (int s = 0; s < n_seq; ++s) {
+    const int L = lens[s] / cfg.block;
+    query_block_pairs(cfg, L, pairs);
+    auto len_of = [&](int q) -> int {  // list length of query block q (table-independent)
+      if (q < 0) return 0;
+      if (cfg.pattern == RT_PATTERN_BAND) {
+        if (q == 0) return L;
+        const int lo = std::max(0, q - cfg.band_half), hi = std::min(L - 1, q + cfg.band_half);
+        return hi - lo + 1 + (lo > 0 ? 1 : 0);
+      }
+      if (!uses_random_table(cfg, L) || q == 0 || q == L - 1) return L;
+      return (q == 1 || q == L - 2 ? 4 : 5) + cfg.num_rand;
+    };
+    for (auto& pr : pairs) {
+      const size_t ub = static_cast<size_t>(len_of(pr.first)) + len_of(pr.second);  // merged list: at most the sum
+      n_items += 1;
+      n_entries += ub;
+      if (split > 0 && ub > static_cast<size_t>(split)) {
+        const size_t parts = ub / split + 2;
+        n_slots += parts;
+        n_items += parts;
+        n_groups += 1;
+      }
+    }
+  }
+  *items = n_items * cfg.heads;
+  *entries = n_entries * cfg.heads;
+  *slots = n_slots * cfg.heads;
+  *groups = n_groups * cfg.heads;
 }
 
 }  // namespace rt

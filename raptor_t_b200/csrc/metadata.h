@@ -107,10 +107,35 @@ using TemplateCache = std::map<std::pair<uint32_t, int>, SeqTemplate>;
 
 rt_status build_seq_template(const rt_config& cfg, uint32_t seed, int n_blocks, TableCache* tables, SeqTemplate& out);
 
+// Where every item of an assembled work list came from, so that the list of another layer of
+// the same batch (same lengths, another table seed) is a refill instead of a new assembly: the
+// query-block pairs, the cuts of long lists and the assignment of items to CTAs depend on the
+// list lengths, which differ between layers only where two random blocks happen to coincide.
+struct PlanSkeleton {
+  struct Src {
+    int32_t seq;        // sequence of the batch
+    int32_t tmpl_item;  // item index inside that sequence's template (head * n_pairs + pair)
+    int32_t part_off;   // offset inside the template item's list
+    int32_t part_len;   // -1: the whole list, else the length of this part of a split list
+  };
+  std::vector<Src> src;  // one per emitted item, in emission (CTA) order
+};
+
 // Assemble the batch work list from per-sequence templates (templates[s] for sequence s)
-// and assign items to CTAs (longest processing time first).
+// and assign items to CTAs (longest processing time first).  skel (optional) records the
+// provenance of every item for refill_attn_plan.
 rt_status assemble_attn_plan(const rt_config& cfg, const int32_t* lens_tokens, int n_seq,
                              const SeqTemplate* const* templates, int n_ctas, AttnPlanHost& out,
-                             int split_entries = kDefaultSplitEntries);
+                             int split_entries = kDefaultSplitEntries, PlanSkeleton* skel = nullptr);
+
+// The work list of another layer of the same batch: items, CTA assignment and cuts of `base`
+// (assembled with `skel`), list entries from that layer's templates.
+rt_status refill_attn_plan(const PlanSkeleton& skel, const AttnPlanHost& base, const SeqTemplate* const* templates,
+                           AttnPlanHost& out);
+
+// Upper bounds of a batch's work-list sizes for any table seed (buffers are sized before the
+// tables exist): work items, list entries, partial-result slots and groups of split lists.
+void attn_plan_bounds(const rt_config& cfg, const int32_t* lens_tokens, int n_seq, int split_entries, size_t* items,
+                      size_t* entries, size_t* slots, size_t* groups);
 
 }  // namespace rt

@@ -13,7 +13,7 @@
 //
 // Limits and rules (also in include/raptor_b200.h):
 //   * at most kMaxItems work items and kMaxEntries list entries per call
-//     (about 26 sequences of 4096 tokens with 12 heads); larger batches are
+//     (25 sequences of 4096 tokens with 12 heads fit); larger batches are
 //     rejected with RT_ERR_UNSUPPORTED and nothing is launched;
 //   * the array is shared by every call on the device and keeps the previous
 //     call's contents: each call overwrites the parts it uses and clears the
@@ -39,7 +39,7 @@
 namespace rt {
 namespace {
 
-constexpr int kMaxItems = 8192;
+constexpr int kMaxItems = 10240;
 constexpr int kMaxEntries = 131072;
 constexpr int kMaxCtas = 1024;
 
@@ -50,7 +50,7 @@ struct StaticScratch {
   int32_t status;  // 0 = ok, otherwise the wait site at which the last kernel gave up
 };
 
-// ~0.78 MB per GPU.  In host code this name is only a handle for the runtime's symbol
+// ~0.84 MB per GPU.  In host code this name is only a handle for the runtime's symbol
 // calls; the device address is obtained once per device below.
 static __device__ __align__(256) unsigned char g_static_scratch[sizeof(StaticScratch)];
 

@@ -35,6 +35,7 @@
 #include <future>
 #include <map>
 #include <mutex>
+#include <optional>
 #include <stdexcept>
 #include <string>
 #include <vector>
@@ -256,10 +257,13 @@ class BertAttention {
     if (pending_.valid()) pending_.wait();
   }
 
-  InfoMap call(const torch::Tensor& input_tensor, const torch::Tensor& /*attention_mask*/, torch::Tensor& output,
-               const std::vector<int> /*seq_position_info*/, torch::Tensor& seq_len_info_tensor,
-               const torch::Tensor& /*partition_part_index_tensor*/, const torch::Tensor& /*partition_part_tensor*/,
-               const int /*block_limit*/, InfoMap& info, bool kernel_fusion, bool /*balanced*/) {
+  // attention_mask and the two partition tensors are not read (the batch is padding-free and the kernel
+  // builds its own work list), so None is accepted for them as well as the tensors the reference passes
+  InfoMap call(const torch::Tensor& input_tensor, const std::optional<torch::Tensor>& /*attention_mask*/,
+               torch::Tensor& output, const std::vector<int> /*seq_position_info*/, torch::Tensor& seq_len_info_tensor,
+               const std::optional<torch::Tensor>& /*partition_part_index_tensor*/,
+               const std::optional<torch::Tensor>& /*partition_part_tensor*/, const int /*block_limit*/, InfoMap& info,
+               bool kernel_fusion, bool /*balanced*/) {
     require_cuda(input_tensor, "input_tensor");
     require_cuda(output, "output");
     TensorSet* ts = TensorSet::get_instance();

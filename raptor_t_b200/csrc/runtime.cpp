@@ -176,6 +176,20 @@ extern "C" rt_status rt_binpack_sequences(const double* cost, int n_seq, int n_b
   return RT_OK;
 }
 
+extern "C" rt_status rt_attn_plan_bounds(const rt_config* cfg, const int32_t* lens, int n_seq, int split_entries,
+                                         int64_t* items, int64_t* entries, int64_t* slots, int64_t* groups) {
+  RT_TRY(check_cfg(cfg));
+  RT_REQUIRE(items && entries && slots && groups, RT_ERR_INVALID, "attn_plan_bounds: null output");
+  RT_TRY(validate_lengths(*cfg, lens, n_seq));
+  size_t a = 0, b = 0, c = 0, d = 0;
+  attn_plan_bounds(*cfg, lens, n_seq, split_entries < 0 ? kDefaultSplitEntries : split_entries, &a, &b, &c, &d);
+  *items = static_cast<int64_t>(a);
+  *entries = static_cast<int64_t>(b);
+  *slots = static_cast<int64_t>(c);
+  *groups = static_cast<int64_t>(d);
+  return RT_OK;
+}
+
 // Host-only construction of the attention work list (no GPU): via the CSR table
 // (use_templates = 0) or via the cached per-sequence templates the encoder uses
 // (use_templates = 1).  items_out holds 8 int32 per item in AttnItem field order.
@@ -190,20 +204,35 @@ extern "C" rt_status rt_attn_plan_build_host(const rt_config* cfg, uint32_t laye
   TableCache tables;
   if (use_templates) {
     TemplateCache cache;
-    std::vector<const SeqTemplate*> tmpl(n_seq);
-    for (int q = 0; q < n_seq; ++q) {
-      const int L = lens[q] / cfg->block;
-      const uint32_t seed = uses_random_table(*cfg, L) ? layer_seed : 0xffffffffu;
-      auto key = std::make_pair(seed, L);
-      auto it = cache.find(key);
-      if (it == cache.end()) {
-        SeqTemplate t;
-        RT_TRY(build_seq_template(*cfg, seed, L, &tables, t));
-        it = cache.emplace(key, std::move(t)).first;
+    auto templates_for = [&](uint32_t seed_of_layer, std::vector<const SeqTemplate*>& tmpl) -> rt_status {
+      tmpl.resize(n_seq);
+      for (int q = 0; q < n_seq; ++q) {
+        const int L = lens[q] / cfg->block;
+        const uint32_t seed = uses_random_table(*cfg, L) ? seed_of_layer : 0xffffffffu;
+        auto key = std::make_pair(seed, L);
+        auto it = cache.find(key);
+        if (it == cache.end()) {
+          SeqTemplate t;
+          RT_TRY(build_seq_template(*cfg, seed, L, &tables, t));
+          it = cache.emplace(key, std::move(t)).first;
+        }
+        tmpl[q] = &it->second;
       }
-      tmpl[q] = &it->second;
+      return RT_OK;
+    };
+    std::vector<const SeqTemplate*> tmpl;
+    if (use_templates == 2) {
+      // the encoder's path for layers after the first: skeleton from another seed's lists, entries refilled
+      PlanSkeleton skel;
+      AttnPlanHost base;
+      RT_TRY(templates_for(layer_seed + 1, tmpl));
+      RT_TRY(assemble_attn_plan(*cfg, lens, n_seq, tmpl.data(), n_ctas, base, kDefaultSplitEntries, &skel));
+      RT_TRY(templates_for(layer_seed, tmpl));
+      RT_TRY(refill_attn_plan(skel, base, tmpl.data(), plan));
+    } else {
+      RT_TRY(templates_for(layer_seed, tmpl));
+      RT_TRY(assemble_attn_plan(*cfg, lens, n_seq, tmpl.data(), n_ctas, plan));
     }
-    RT_TRY(assemble_attn_plan(*cfg, lens, n_seq, tmpl.data(), n_ctas, plan));
   } else {
     BlockCsr csr;
     RT_TRY(build_block_csr(*cfg, layer_seed, lens, n_seq, csr, &tables));

@@ -159,6 +159,12 @@ class Encoder:
             out[key] = float(ms.value)
         return out
 
+    def host_blocked_ms(self):
+        """Cumulative time the calling thread spent waiting for the GPU to release a slot or buffer."""
+        ms = C.c_float()
+        check(lib.rt_encoder_get_timing(self._h, b"host_blocked", C.byref(ms)))
+        return float(ms.value)
+
     def close(self):
         if self._h:
             lib.rt_encoder_destroy(self._h)

@@ -101,3 +101,11 @@ def attention_plan_host(cfg, layer_seed, lens_tokens, n_ctas, use_templates=True
                                       items.ctypes.data_as(i32p), ni.value, entries.ctypes.data_as(i32p), ne.value,
                                       cta_ptr.ctypes.data_as(i32p), C.byref(ni), C.byref(ne), C.byref(vis)))
     return {"items": items, "entries": entries, "cta_ptr": cta_ptr, "visits": int(vis.value)}
+
+
+def attention_plan_bounds(cfg, lens_tokens, split_entries=-1):
+    """Upper bounds of a batch's work-list sizes for any table seed: dict(items, entries, slots, groups)."""
+    lens, lp = _i32(lens_tokens)
+    out = [C.c_int64() for _ in range(4)]
+    check(lib.rt_attn_plan_bounds(C.byref(cfg), lp, len(lens), int(split_entries), *[C.byref(o) for o in out]))
+    return dict(zip(("items", "entries", "slots", "groups"), (int(o.value) for o in out)))

@@ -2,6 +2,12 @@
 weights, no collective inside the layers), each rank runs its share, and one
 variable-size gather of the final hidden states restores input order.
 
+Two forms of that gather: RootGatherer delivers the batch to ONE rank (the caller that
+submitted it) - every rank sends each of its sequences straight to that sequence's rows of
+the root's output buffer, so no padding, no permutation pass and 1/N of an all-gather's
+traffic; OutputGatherer / gather_outputs leave the full output on every rank (padded
+all_gather + one index_select).
+
 The reference has no multi-GPU path; this lifts its longest-processing-time greedy
 (python/util.py:11-34, used there across CTAs) to GPUs.
 """
@@ -124,6 +130,91 @@ class OutputGatherer:
 
     def finish(self, ticket):
         """Makes the current stream wait for that gather and returns its result buffer."""
+        if self.cuda:
+            torch.cuda.current_stream().wait_event(self.done[ticket])
+        return self.out[ticket]
+
+
+class RootGatherer:
+    """Gather of one batch layout to a single rank, set up once.  A sequence's rows are a
+    contiguous range of the packed output in input order, so every rank sends each of its
+    sequences as one message and the root receives it in place (grouped send/recv: one NCCL
+    group per gather).  The root's own sequences are local copies.  On CUDA the gather runs on a
+    side stream (start()/finish()), `depth` result buffers rotate; finish() returns the
+    [T_total, H] tensor on the root and None elsewhere."""
+
+    def __init__(self, assignment, lens_tokens, hidden, dtype, device, group=None, depth=2, root=0):
+        self.group, self.root = group, root
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.device = torch.device(device)
+        self.starts = np.concatenate([[0], np.cumsum(lens_tokens)]).astype(np.int64)
+        self.total = int(self.starts[-1])
+        self.lens = [int(n) for n in lens_tokens]
+        self.assignment = [list(a) for a in assignment]
+        self.local_tokens = sum(self.lens[i] for i in self.assignment[self.rank])
+        self.is_root = self.rank == root
+        self.out = ([torch.empty(self.total, hidden, dtype=dtype, device=self.device) for _ in range(depth)]
+                    if self.is_root else [None] * depth)
+        self.cuda = self.device.type == "cuda"
+        self.side = torch.cuda.Stream(device=self.device) if self.cuda else None
+        self.done = [torch.cuda.Event() for _ in range(depth)] if self.cuda else None
+        self.n = 0
+
+    def _run(self, local_out, k):
+        ops = []
+        if self.is_root:
+            out = self.out[k]
+            for r, seqs in enumerate(self.assignment):
+                off = 0
+                for i in seqs:
+                    n, s0 = self.lens[i], int(self.starts[i])
+                    if r == self.rank:
+                        out[s0:s0 + n].copy_(local_out[off:off + n])
+                    else:
+                        ops.append(dist.P2POp(dist.irecv, out[s0:s0 + n], r, group=self.group))
+                    off += n
+        else:
+            off = 0
+            for i in self.assignment[self.rank]:
+                n = self.lens[i]
+                ops.append(dist.P2POp(dist.isend, local_out[off:off + n], self.root, group=self.group))
+                off += n
+        if ops:
+            for req in dist.batch_isend_irecv(ops):
+                req.wait()
+        return self.out[k]
+
+    def gather(self, local_out):
+        """Synchronous with the current stream."""
+        k = self.n % len(self.out)
+        self.n += 1
+        return self._run(local_out, k)
+
+    def start(self, local_out, host_out=None):
+        """Enqueue the gather behind the work already on the current stream, on the side stream;
+        returns a ticket for finish().  local_out must stay untouched until then.  host_out
+        (root only, pinned [>= T_total, H]): the gathered batch is also copied there, still on the
+        side stream, so the device-to-host copy overlaps the next steps' kernels as well."""
+        k = self.n % len(self.out)
+        self.n += 1
+        if not self.cuda:
+            full = self._run(local_out, k)
+            if host_out is not None and full is not None:
+                host_out[: self.total].copy_(full)
+            return k
+        ready = torch.cuda.Event()
+        ready.record()
+        with torch.cuda.stream(self.side):
+            self.side.wait_event(ready)
+            full = self._run(local_out, k)
+            if host_out is not None and full is not None:
+                host_out[: self.total].copy_(full, non_blocking=True)
+            self.done[k].record()
+        return k
+
+    def finish(self, ticket):
+        """Makes the current stream wait for that gather; the result buffer on the root, None elsewhere."""
         if self.cuda:
             torch.cuda.current_stream().wait_event(self.done[ticket])
         return self.out[ticket]

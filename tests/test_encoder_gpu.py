@@ -101,6 +101,27 @@ def test_large_shape_layers_within_tolerance():
     enc.close()
 
 
+def test_wide_band_encoder_where_most_lists_are_cut():
+    """Band pattern with a window of 33 blocks on a small batch: nearly every key/value list is
+    longer than the cut threshold, so the work list has about one group of parts per item."""
+    _skip_no_gpu()
+    cfg = EncoderConfig(hidden=128, heads=2, ffn=256, layers=2, max_pos=4096, vocab=97, pattern="band", band_half=16)
+    P = oracle.make_weights(cfg, seed=11, nonzero_bias=True)
+    enc = _make(cfg, torch.float16, P)
+    lens = [2048, 640]
+    rng = np.random.default_rng(2)
+    seqs = [torch.from_numpy(rng.integers(0, cfg.vocab, size=n)).int() for n in lens]
+    ref = oracle.encoder_ref(seqs, P, cfg)
+    enc.prepare(lens)
+    out = enc.forward_ids(torch.cat(seqs).cuda())
+    from raptor_t_b200 import ops
+    ops.check_device()
+    err = (out.float().cpu() - ref).abs()
+    print(f"PARITY wide_band max_abs={err.max().item():.5f} mean_abs={err.mean().item():.6f}")
+    assert err.max().item() < MAX_ABS and err.mean().item() < MEAN_ABS, (err.max().item(), err.mean().item())
+    enc.close()
+
+
 def test_forward_host_matches_device_path_and_repeats():
     _skip_no_gpu()
     cfg = EncoderConfig(hidden=128, heads=2, ffn=256, layers=2, max_pos=4096, vocab=97)

@@ -113,7 +113,7 @@ def test_binpack_matches_oracle():
 @pytest.mark.parametrize("pattern,lens", [("bigbird", [1024, 832, 4096, 512, 704, 1984, 64, 128]),
                                           ("band", [1280, 64, 512, 2048]), ("bigbird", [960]),
                                           ("bigbird", [4096]), ("bigbird", [2048, 4096])])
-@pytest.mark.parametrize("use_templates", [0, 1])
+@pytest.mark.parametrize("use_templates", [0, 1, 2])
 def test_attention_work_list_covers_every_block_list_once(pattern, lens, use_templates):
     """Every (sequence, head, query block) appears in exactly one work item and the masked
     entries of that item reproduce its key/value list as a multiset."""
@@ -141,9 +141,9 @@ def test_attention_work_list_covers_every_block_list_once(pattern, lens, use_tem
     for q_row0, q_row1, kv_row0, off, n_ent, tok0, tok1, head_field in items.tolist():
         head, slot = head_field & 255, (head_field >> 8) - 1
         if slot >= 0:
-            # one part of a split list: no longer than 24 entries or one CTA's share of the batch,
-            # and with a scratch slot of its own
-            assert n_ent <= max(24, -(-(len(entries) + 2 * len(items)) // n_ctas)) and slot not in slots
+            # one part of a split list: no longer than 24 entries or one CTA's share of the batch
+            # (+1: parts are whole two-entry steps), and with a scratch slot of its own
+            assert n_ent <= max(24, -(-(len(entries) + 2 * len(items)) // n_ctas)) + 1 and slot not in slots
             slots.add(slot)
         s = int(np.searchsorted(starts, tok0, side="right") - 1)
         n = lens[s]
@@ -184,3 +184,38 @@ def test_template_and_csr_work_lists_agree():
     b = metadata.attention_plan_host(cfg, 1, lens, 296, 1)
     assert np.array_equal(a["items"], b["items"]) and np.array_equal(a["entries"], b["entries"])
     assert np.array_equal(a["cta_ptr"], b["cta_ptr"]) and a["visits"] == b["visits"]
+
+
+@pytest.mark.parametrize("pattern,band_half,lens", [
+    ("bigbird", 4, [1024, 832, 4096, 512, 704, 1984, 64, 128]), ("bigbird", 4, [4096]), ("bigbird", 4, [832] * 40),
+    ("band", 4, [1280, 64, 512, 2048]), ("band", 11, [2048]), ("band", 16, [2048, 640]), ("band", 40, [4096, 64]),
+    ("band", 0, [1024])])
+def test_work_list_size_bounds_hold(pattern, band_half, lens):
+    """The encoder sizes its metadata regions before the tables exist: the bounds must cover the
+    work list of every layer seed, also for band windows so wide that most lists are cut."""
+    o = EncoderConfig(pattern=pattern, band_half=band_half)
+    cfg = _cfg(o)
+    bounds = metadata.attention_plan_bounds(cfg, lens)
+    for seed in (0, 5):
+        for n_ctas in (296, 16):
+            plan = metadata.attention_plan_host(cfg, seed, lens, n_ctas, 1)
+            items = plan["items"]
+            slots = {(h >> 8) - 1 for h in items[:, 7].tolist() if (h >> 8) > 0}
+            groups = {(int(t0), int(h) & 255) for t0, h in zip(items[:, 5], items[:, 7]) if (h >> 8) > 0}
+            assert len(items) <= bounds["items"] and len(plan["entries"]) <= bounds["entries"]
+            assert len(slots) <= bounds["slots"] and len(groups) <= bounds["groups"], (len(slots), len(groups), bounds)
+
+
+def test_static_entry_capacity_statement():
+    """The no-allocation attention entry point documents room for 25 sequences of 4096 tokens with
+    12 heads (10240 work items, 131072 list entries, lists never cut): check it against the builder."""
+    o = EncoderConfig()
+    cfg = _cfg(o)
+    lens = [4096] * 25
+    kv_ptr, kv_idx = metadata.build_block_csr(cfg, 0, lens)
+    ni, ne = 0, 0
+    plan = metadata.attention_plan_host(cfg, 0, lens, 296, 0)
+    whole = {}
+    for q0, q1, kv0, off, n, t0, t1, h in plan["items"].tolist():   # undo the cuts: count whole lists
+        whole[(t0, h & 255)] = whole.get((t0, h & 255), 0) + n
+    assert len(whole) <= 10240 and sum(whole.values()) <= 131072

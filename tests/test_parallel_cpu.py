@@ -37,6 +37,15 @@ def _worker(rank, world, port, lens, H):
     t1 = g.start(local)
     t2 = g.start(local * 2)
     assert torch.equal(g.finish(t1), exp) and torch.equal(g.finish(t2), exp * 2)
+    # gather to one rank: grouped send/recv straight into the root's rows, nothing on the others
+    for root in (0, world - 1):
+        rg = parallel.RootGatherer(assignment, lens, H, torch.float32, "cpu", root=root)
+        for scale in (1.0, 3.0):
+            got = rg.finish(rg.start(local * scale))
+            if rank == root:
+                assert torch.equal(got, exp * scale)
+            else:
+                assert got is None
     dist.destroy_process_group()
 
 
