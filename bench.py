@@ -465,7 +465,7 @@ def run_gpu(args, w):
     print(json.dumps({
         "metric": "encoder_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": n_gpus,
         "steps": args.steps, "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+        "scaling": w.get("scaling", "weak"), "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
         "config": {"workload": w["desc"], "sequences": len(batches[0].lens_all), "tokens": batches[0].T_total,
                    "rotation": f"{N_ROTATE} batches (seeds 0..{N_ROTATE - 1}, {[b.T_total for b in batches]} tokens) take turns; "
                                f"tokens/s counts the tokens of the steps actually timed",
@@ -504,12 +504,22 @@ def main():
     ap.add_argument("--workload", default="base", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--seqs", type=int, default=0, help="sequences per GPU (default: the workload's own count)")
+    ap.add_argument("--total-seqs", type=int, default=0,
+                    help="strong scaling: this many sequences in the global batch whatever --gpus (must divide evenly)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     w = WORKLOADS[args.workload]
     if args.seqs > 0:
         w["seqs"] = args.seqs
         w["desc"] += f" (--seqs {args.seqs})"
+    w["scaling"] = "weak"
+    if args.total_seqs > 0:
+        world = int(os.environ.get("WORLD_SIZE", "1")) if args.impl == "ours" else 1
+        if args.total_seqs % world:
+            raise SystemExit("--total-seqs must be a multiple of the number of GPUs")
+        w["seqs"] = args.total_seqs // world
+        w["scaling"] = "strong"
+        w["desc"] += f" (fixed global batch of {args.total_seqs} sequences)"
     if args.impl == "reference":
         run_reference(args, w)
     else:
