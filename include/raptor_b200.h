@@ -135,6 +135,15 @@ rt_status rt_gemm(void* c_dev, const void* a_dev, const void* w_dev, const void*
 rt_status rt_gemm_residual(void* c_dev, const void* a_dev, const void* w_dev, const void* bias_dev,
                            const void* residual_dev, int M, int N, int K, int dtype, void* stream);
 
+/* out[M][N] = LayerNorm(A W^T + bias + residual) * gamma + beta in ONE kernel, N = 768 or 1024: the
+ * projection and the add_bias_and_layernorm kernel that follows it in both sub-layers
+ * (layers/multi_headed_attention.cpp:206-210, layers/bert_output.cpp:19-23).  A cluster of N/256 CTA
+ * pairs owns 256 whole rows; the pre-LayerNorm sum stays in fp32 in TMEM and never reaches HBM.
+ * All pointers 32-byte aligned, K % 64 == 0; out may alias residual. */
+rt_status rt_gemm_bias_residual_layernorm(void* out_dev, const void* a_dev, const void* w_dev, const void* bias_dev,
+                                          const void* residual_dev, const void* gamma_dev, const void* beta_dev,
+                                          int M, int N, int K, float eps, int dtype, void* stream);
+
 /* Fused QKV projection: (A[M][K] * W[3*heads*64][K]^T + bias), query part scaled by q_scale,
  * written head-major per sequence straight into q/k/v (the layout of rt_qkv_bias_transpose) -
  * the [T][3H] intermediate of layers/multi_headed_attention.cpp:143-152 (FuseGemm012AddBIasTranspose)
@@ -277,9 +286,12 @@ rt_status rt_encoder_get_timing(rt_encoder* enc, const char* key, float* ms_out)
 rt_status rt_encoder_enable_timing(rt_encoder* enc, int on);
 rt_status rt_encoder_kernel_launches(rt_encoder* enc, int64_t* launches_out);
 /* options: "fuse_gelu" (1: bias+GELU in the FFN-up GEMM epilogue, 0: separate rt_bias_gelu kernel);
- * "fuse_qkv" (1: rt_gemm_qkv, 0: rt_gemm + rt_qkv_bias_transpose); "fuse_residual" (1: bias + residual
- * added in the projection GEMM's epilogue, LayerNorm reads one tensor; default 0: it costs one more 16-bit
- * rounding and measured slower).  fuse_gelu and fuse_qkv default to 1. */
+ * "fuse_qkv" (1: rt_gemm_qkv, 0: rt_gemm + rt_qkv_bias_transpose); "fuse_layernorm" (LayerNorm in the epilogue of
+ * the hidden-wide projections, rt_gemm_bias_residual_layernorm: 0 never; 1 where it measured faster, i.e.
+ * the FFN-down projection of a 768-wide model; 2 both projections of 768- and 1024-wide models);
+ * "fuse_residual" (1: bias + residual added in the projection GEMM's epilogue, LayerNorm reads one tensor;
+ * default 0: it costs one more 16-bit rounding and measured slower; ignored where fuse_layernorm applies).
+ * fuse_gelu, fuse_qkv and fuse_layernorm default to 1. */
 rt_status rt_encoder_set_option(rt_encoder* enc, const char* name, int value);
 /* work-list statistics of one layer of the prepared batch */
 rt_status rt_encoder_plan_stats(rt_encoder* enc, int layer, int64_t* entries_out, int64_t* visits_out,

@@ -17,7 +17,7 @@ LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libraptor_b200.so")
 
 SOURCES = [
-    "runtime.cpp", "metadata.cpp", "tma_host.cpp", "elementwise.cu", "gemm_sm100.cu", "gemm_pair_sm100.cu", "attention_sm100.cu",
+    "runtime.cpp", "metadata.cpp", "tma_host.cpp", "elementwise.cu", "gemm_sm100.cu", "gemm_pair_sm100.cu", "gemm_ln_sm100.cu", "attention_sm100.cu",
     "encoder.cu", "no_alloc.cu", "selftest.cu",
 ]
 

@@ -60,6 +60,7 @@ _SIGS = {
     "rt_embeddings": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_float, C.c_int, _vp]),
     "rt_gemm": (C.c_int, [_vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp]),
     "rt_gemm_residual": (C.c_int, [_vp, _vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, _vp]),
+    "rt_gemm_bias_residual_layernorm": (C.c_int, [_vp] * 7 + [C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, _vp]),
     "rt_gemm_qkv": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, _vp]),
     "rt_attn_plan_create": (C.c_int, [_cfgp, _i32p, C.c_int, _i32p, _i32p, C.c_int, C.c_int, _vp, C.POINTER(_vp)]),
     "rt_attn_plan_destroy": (C.c_int, [_vp]),

@@ -120,6 +120,10 @@ struct rt_encoder {
   bool emb_set = false;
   bool fuse_gelu = true;
   bool fuse_qkv = true;
+  // LayerNorm in the epilogue of the hidden-wide projections (rt_gemm_bias_residual_layernorm):
+  // 0 never, 1 where it measured faster (FFN-down of a 768-wide model: long K, three column tiles), 2 wherever
+  // the kernel exists (hidden 768 / 1024, both projections)
+  int fuse_layernorm = 1;
   bool fuse_residual = false;  // measured slower on B200 (GEMM epilogue cost > LayerNorm saving); kept as an option
 
   // scratch ("TensorSet")
@@ -413,7 +417,11 @@ rt_status run_attention(rt_encoder* e, int l, const void* input, void* output, c
                                    AttnSplit{reinterpret_cast<const int32_t*>(dev + e->groups_off), e->plan_groups[l],
                                              static_cast<float*>(e->part_o.p), static_cast<float*>(e->part_ml.p)}));
   }
-  if (e->fuse_residual) {
+  if (e->fuse_layernorm == 2 && (H == 768 || H == 1024)) {
+    Span s(e, st, "gemm.attention_output");
+    RT_TRY(rt_gemm_bias_residual_layernorm(output, ctx, w.ao_w.p, w.ao_b.p, input, w.aln_g.p, w.aln_b.p, T, H, H, c.eps,
+                                           dt, st));
+  } else if (e->fuse_residual) {
     {
       Span s(e, st, "gemm.attention_output");
       RT_TRY(rt_gemm_residual(dense, ctx, w.ao_w.p, w.ao_b.p, input, T, H, H, dt, st));
@@ -454,6 +462,12 @@ rt_status run_output(rt_encoder* e, int l, const void* ffn, const void* residual
   LayerWeights& w = e->layers[l];
   RT_REQUIRE(w.set, RT_ERR_STATE, "layer %d has no weights", l);
   void* dense = e->scratch["dense_out"].p;
+  if ((e->fuse_layernorm == 2 && (c.hidden == 768 || c.hidden == 1024)) ||
+      (e->fuse_layernorm == 1 && c.hidden == 768 && c.ffn >= 2048)) {
+    Span s(e, st, "gemm.ffn_down");
+    return rt_gemm_bias_residual_layernorm(out, ffn, w.down_w.p, w.down_b.p, residual, w.oln_g.p, w.oln_b.p, e->tokens,
+                                           c.hidden, c.ffn, c.eps, c.dtype, st);
+  }
   if (e->fuse_residual) {
     {
       Span s(e, st, "gemm.ffn_down");
@@ -629,6 +643,11 @@ extern "C" rt_status rt_encoder_set_option(rt_encoder* e, const char* name, int 
   }
   if (std::strcmp(name, "fuse_qkv") == 0) {
     e->fuse_qkv = value != 0;
+    return RT_OK;
+  }
+  if (std::strcmp(name, "fuse_layernorm") == 0) {
+    RT_REQUIRE(value >= 0 && value <= 2, RT_ERR_INVALID, "set_option: fuse_layernorm takes 0, 1 or 2");
+    e->fuse_layernorm = value;
     return RT_OK;
   }
   if (std::strcmp(name, "fuse_residual") == 0) {

@@ -6,6 +6,7 @@ python/benchmark/attention_test.py and mem_bound_op.py, re-stated for this libra
     python -m raptor_t_b200.microbench --kernel gelu --rows 32768 --cols 3072
     python -m raptor_t_b200.microbench --kernel transpose --seq 4096 --batch 8
     python -m raptor_t_b200.microbench --kernel gemm --m 16384 --n 3072 --k 768
+    python -m raptor_t_b200.microbench --kernel gemm_ln --m 16384 --n 768 --k 3072
     python -m raptor_t_b200.microbench --kernel all
 
 Each line of output is one JSON object: algorithmic FLOPs or bytes, the median CUDA-event
@@ -139,10 +140,32 @@ def bench_gemm(m, n, k, dtype, iters, epilogue=capi.RT_EPI_NONE):
             "peak_source": src}
 
 
+def bench_gemm_ln(m, n, k, dtype, iters):
+    """Projection + bias + residual + LayerNorm in one kernel, next to the two-kernel path it replaces."""
+    hbm, tf, src = _peaks()
+    dt = _dtype(dtype)
+    a = torch.randn(m, k, device="cuda").to(dt)
+    w = (torch.randn(n, k, device="cuda") / math.sqrt(k)).to(dt)
+    bias, gamma, beta = (torch.randn(n, device="cuda").to(dt) for _ in range(3))
+    res = torch.randn(m, n, device="cuda").to(dt)
+    out = torch.empty(m, n, device="cuda", dtype=dt)
+    dense = torch.empty(m, n, device="cuda", dtype=dt)
+    med, best = _time(lambda: ops.gemm_bias_residual_layernorm(a, w, bias, res, gamma, beta, 1e-12, out=out), iters)
+
+    def two():
+        ops.gemm(a, w, out=dense)
+        ops.bias_residual_layernorm(dense, bias, res, gamma, beta, 1e-12, out=out)
+    med2, _ = _time(two, iters)
+    flops = 2.0 * m * n * k
+    return {"kernel": "gemm_bias_residual_layernorm", "m": m, "n": n, "k": k, "dtype": dtype, "flops": flops, "ms": med,
+            "ms_min": best, "tflops": flops / med / 1e9, "frac_of_tensor_peak": flops / med / 1e9 / tf,
+            "two_kernel_ms": med2, "peak": tf, "peak_source": src}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernel", default="all",
-                    choices=["all", "attention", "layernorm", "gelu", "transpose", "gemm", "attention_sweep"])
+                    choices=["all", "attention", "layernorm", "gelu", "transpose", "gemm", "gemm_ln", "attention_sweep"])
     ap.add_argument("--seq", type=int, default=4096)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--heads", type=int, default=12)
@@ -174,6 +197,8 @@ def main():
         out.append(bench_transpose(a.seq, a.batch, a.dtype, a.iters, a.heads))
     if a.kernel == "gemm":
         out.append(bench_gemm(a.m, a.n, a.k, a.dtype, a.iters))
+    if a.kernel == "gemm_ln":
+        out.append(bench_gemm_ln(a.m, a.n, a.k, a.dtype, a.iters))
     if a.kernel == "all":
         out.append(bench_layernorm(32768, 768, a.dtype, a.iters))
         out.append(bench_layernorm(32768, 1024, a.dtype, a.iters))
@@ -182,6 +207,8 @@ def main():
         for (m, n, k) in ((16384, 2304, 768), (16384, 768, 768), (16384, 3072, 768), (16384, 768, 3072)):
             out.append(bench_gemm(m, n, k, a.dtype, a.iters))
         out.append(bench_gemm(16384, 3072, 768, a.dtype, a.iters, capi.RT_EPI_BIAS_GELU))
+        for (m, n, k) in ((16384, 768, 768), (16384, 768, 3072), (16384, 1024, 4096)):
+            out.append(bench_gemm_ln(m, n, k, a.dtype, a.iters))
     for o in out:
         print(json.dumps(o), flush=True)
 

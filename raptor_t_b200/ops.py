@@ -88,6 +88,17 @@ def gemm_residual(a, w, bias, residual, out=None):
     return out
 
 
+def gemm_bias_residual_layernorm(a, w, bias, residual, gamma, beta, eps, out=None):
+    """out[M,N] = LayerNorm(a @ w^T + bias + residual) * gamma + beta in one kernel (N = 768 or 1024)."""
+    M, K = a.shape
+    N = w.shape[0]
+    if out is None:
+        out = torch.empty(M, N, dtype=a.dtype, device=a.device)
+    check(lib.rt_gemm_bias_residual_layernorm(_p(out), _p(a), _p(w), _p(bias), _p(residual), _p(gamma), _p(beta), M, N, K,
+                                              float(eps), _dt(a), _stream()))
+    return out
+
+
 def block_seq_table(lens_tokens, device="cuda"):
     """int32 [N, 2]: for every packed 64-token block {first token of its sequence, sequence length}."""
     import numpy as np

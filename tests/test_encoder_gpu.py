@@ -76,6 +76,30 @@ def test_base_encoder_hidden_states_within_tolerance():
         enc.close()
 
 
+def test_fused_layernorm_projection_matches_the_two_kernel_path():
+    """Base dimensions, 2 layers: the hidden-wide projections with LayerNorm in their epilogue (default)
+    against the same encoder with a separate LayerNorm kernel, and both against the oracle."""
+    _skip_no_gpu()
+    cfg = EncoderConfig(layers=2, vocab=1000)
+    P = oracle.make_weights(cfg, seed=2, nonzero_bias=True)
+    lens = [1088, 320, 2048]
+    rng = np.random.default_rng(4)
+    seqs = [torch.from_numpy(rng.integers(5, cfg.vocab, size=n)).int() for n in lens]
+    ref = oracle.encoder_ref(seqs, P, cfg)
+    outs = {}
+    for fused in (2, 1, 0):
+        enc = _make(cfg, torch.float16, P)
+        enc.set_option("fuse_layernorm", fused)
+        enc.prepare(lens)
+        outs[fused] = enc.forward_ids(torch.cat(seqs).cuda()).clone()
+        err = (outs[fused].float().cpu() - ref).abs()
+        print(f"PARITY fuse_layernorm={fused} max_abs={err.max().item():.5f} mean_abs={err.mean().item():.6f}")
+        assert err.max().item() < MAX_ABS and err.mean().item() < MEAN_ABS, (fused, err.max().item(), err.mean().item())
+        enc.close()
+    assert (outs[2].float() - outs[0].float()).abs().max().item() < MAX_ABS
+    assert (outs[1].float() - outs[0].float()).abs().max().item() < MAX_ABS
+
+
 def test_large_shape_layers_within_tolerance():
     """BigBird-large dimensions (hidden 1024, 16 heads, FFN 4096, 8192 positions), two layers, a
     batch with a sparse, a full-attention and a long sequence: every GEMM shape, the 1024-wide

@@ -158,6 +158,33 @@ def test_gemm_residual(ops, dtype, M, N, K):
     ops.check_device()
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K", [(256, 768, 768), (1000, 768, 3072), (16512, 768, 768), (64, 1024, 1024),
+                                   (4100, 1024, 4096), (1, 768, 64)])
+def test_gemm_bias_residual_layernorm(ops, dtype, M, N, K):
+    """Projection + bias + residual + LayerNorm in one kernel (clusters of N/256 CTA pairs own whole
+    rows) against torch fp32; also in place over the residual, and against the two-kernel path."""
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    a = torch.randn(M, K, device="cuda", generator=g).to(dtype)
+    w = (torch.randn(N, K, device="cuda", generator=g) / math.sqrt(K)).to(dtype)
+    b = (0.1 * torch.randn(N, device="cuda", generator=g)).to(dtype)
+    r = torch.randn(M, N, device="cuda", generator=g).to(dtype)
+    gamma = (1 + 0.1 * torch.randn(N, device="cuda", generator=g)).to(dtype)
+    beta = (0.1 * torch.randn(N, device="cuda", generator=g)).to(dtype)
+    x = a.float() @ w.float().t() + b.float() + r.float()
+    ref = torch.nn.functional.layer_norm(x, (N,), gamma.float(), beta.float(), 1e-12)
+    out = ops.gemm_bias_residual_layernorm(a, w, b, r, gamma, beta, 1e-12)
+    err = (out.float() - ref).abs()
+    assert err.max().item() < _tol(dtype) * 2 and err.mean().item() < _tol(dtype) / 8, (err.max().item(), err.mean().item())
+    two = ops.bias_residual_layernorm(ops.gemm(a, w), b, r, gamma, beta, 1e-12)   # rounds the projection to 16 bits first
+    assert (out.float() - two.float()).abs().max().item() < _tol(dtype) * 2
+    inplace = ops.gemm_bias_residual_layernorm(a, w, b, r, gamma, beta, 1e-12, out=r)   # output over the residual buffer
+    assert torch.equal(inplace, out)
+    again = ops.gemm_bias_residual_layernorm(a, w, b, out.clone(), gamma, beta, 1e-12)    # another launch, other data
+    assert torch.isfinite(again.float()).all()
+    ops.check_device()
+
+
 def _attention_case(ops, dtype, cfg, lens, layer, seed):
     from raptor_t_b200 import capi, metadata
     rc = capi.make_config(hidden=cfg.hidden, heads=cfg.heads, ffn=cfg.ffn, layers=cfg.layers, max_pos=cfg.max_pos,
