@@ -346,6 +346,7 @@ def run_gpu(args, w):
     pipe["i"] = 0
     stage_flops = [0.0, 0.0]
     stage_tokens = 0
+    ln_in_ao, ln_in_down = enc.layernorm_in_projection()
     for i in range(args.steps):
         flush.fill_(1)
         b = step()
@@ -425,20 +426,33 @@ def run_gpu(args, w):
         return
 
     # ---- roofline of the dominant kernel (this rank's share, summed over the timed steps) --------
+    # gemm_pair_kernel = the projections whose span holds nothing but the GEMM and its bias / GELU / QKV
+    # epilogue; a projection that carries its LayerNorm (gemm_ln_kernel) is reported beside it, because its
+    # span also contains the LayerNorm's work, which is not counted as FLOPs.
     pk = peaks()
-    gemm_fl, attn_fl = stage_flops
-    n_gemm = 4 * w["layers"] * args.steps
-    n_attn = w["layers"] * args.steps
-    gemm_ms, attn_ms = stage_ms.get("gemm", 0.0), stage_ms.get("attention", 0.0)
+    H, F, L = w["hidden"], w["ffn"], w["layers"]
+    fl = {"gemm.qkv": 2.0 * H * 3 * H, "gemm.attention_output": 2.0 * H * H, "gemm.ffn_up": 2.0 * H * F,
+          "gemm.ffn_down": 2.0 * F * H}
+    fl = {k: v * L * stage_tokens for k, v in fl.items()}
+    fused_keys = [k for k, on in (("gemm.attention_output", ln_in_ao), ("gemm.ffn_down", ln_in_down)) if on]
+    pair_keys = [k for k in fl if k not in fused_keys]
+    gemm_fl, attn_fl = sum(fl[k] for k in pair_keys), stage_flops[1]
+    gemm_ms = sum(stage_ms.get(k, 0.0) for k in pair_keys)
+    n_gemm = len(pair_keys) * L * args.steps
+    n_attn = L * args.steps
+    attn_ms = stage_ms.get("attention", 0.0)
     ln_ms, tr_ms = stage_ms.get("add_bias_and_layernorm_kernel", 0.0), stage_ms.get("add_bias_and_transpose_kernel", 0.0)
     per = {k: v / args.steps for k, v in stage_ms.items()}
     gemm_tf = gemm_fl / (gemm_ms * 1e-3) / 1e12 if gemm_ms else 0.0
     attn_tf = attn_fl / (attn_ms * 1e-3) / 1e12 if attn_ms else 0.0
-    ln_gbs = (2 * w["layers"] * 3 * stage_tokens * w["hidden"] * 2) / (ln_ms * 1e-3) / 1e9 if ln_ms else 0.0
-    tr_gbs = (w["layers"] * 2 * stage_tokens * 3 * w["hidden"] * 2) / (tr_ms * 1e-3) / 1e9 if tr_ms else 0.0
+    fused_ms = sum(stage_ms.get(k, 0.0) for k in fused_keys)
+    fused_tf = sum(fl[k] for k in fused_keys) / (fused_ms * 1e-3) / 1e12 if fused_ms else 0.0
+    ln_launches = L * (2 - len(fused_keys))
+    ln_gbs = (ln_launches * 3 * stage_tokens * H * 2) / (ln_ms * 1e-3) / 1e9 if ln_ms else 0.0
+    tr_gbs = (L * 2 * stage_tokens * 3 * H * 2) / (tr_ms * 1e-3) / 1e9 if tr_ms else 0.0
     if gemm_ms >= attn_ms:
-        roof = {"kernel": "gemm_pair_kernel (CTA-pair tcgen05 projection GEMMs, 4 per layer)", "bound": "tensor",
-                "achieved": gemm_tf, "peak": pk["tf_sustained"], "unit": "TFLOP/s",
+        roof = {"kernel": f"gemm_pair_kernel (CTA-pair tcgen05 projection GEMMs: {', '.join(k[5:] for k in pair_keys)})",
+                "bound": "tensor", "achieved": gemm_tf, "peak": pk["tf_sustained"], "unit": "TFLOP/s",
                 "frac": gemm_tf / pk["tf_sustained"], "traffic": ncu_traffic("gemm", gemm_fl / n_gemm),
                 "launches_per_step": n_gemm // args.steps, "avg_launch_ms": gemm_ms / n_gemm,
                 "flops_per_launch": gemm_fl / n_gemm}
@@ -486,6 +500,9 @@ def run_gpu(args, w):
         "rooflines_other": {
             "attention_tflops": attn_tf, "attention_frac_of_tensor_peak": attn_tf / pk["tf_sustained"],
             "gemm_tflops": gemm_tf,
+            "gemm_with_layernorm_tflops": fused_tf,
+            "gemm_with_layernorm": [k[5:] for k in fused_keys],
+            "layernorm_launches_per_step": ln_launches,
             "layernorm_gbs": ln_gbs, "layernorm_frac_of_hbm": ln_gbs / pk["hbm"],
             "qkv_transpose_gbs": tr_gbs, "qkv_transpose_frac_of_hbm": tr_gbs / pk["hbm"],
         },

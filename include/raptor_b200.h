@@ -293,6 +293,7 @@ rt_status rt_encoder_kernel_launches(rt_encoder* enc, int64_t* launches_out);
  * default 0: it costs one more 16-bit rounding and measured slower; ignored where fuse_layernorm applies).
  * fuse_gelu, fuse_qkv and fuse_layernorm default to 1. */
 rt_status rt_encoder_set_option(rt_encoder* enc, const char* name, int value);
+rt_status rt_encoder_get_option(rt_encoder* enc, const char* name, int* value_out);
 /* work-list statistics of one layer of the prepared batch */
 rt_status rt_encoder_plan_stats(rt_encoder* enc, int layer, int64_t* entries_out, int64_t* visits_out,
                                 int32_t* items_out);

@@ -1,7 +1,10 @@
 """Recipe for oracle/_ref/: puts the reference's validation module where oracle/ref_runner.py
 loads it from.
 
-    python oracle/build_ref.py [/path/to/reference]      (default: /root/reference)
+    python oracle/build_ref.py [/path/to/reference]
+
+Without an argument the checkout is looked for in $RAPTOR_T_REFERENCE and then in a directory named
+`reference` beside this repository.
 
 The reference's path is Python, so "building" it is taking python/modeling_big_bird.py as it
 lies in the checkout; nothing is edited.  oracle/_ref/ is git-ignored: the file never enters
@@ -16,8 +19,15 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def build(ref_root="/root/reference"):
-    src = os.path.join(ref_root, "python", "modeling_big_bird.py")
+def _default_root():
+    env = os.environ.get("RAPTOR_T_REFERENCE")
+    if env:
+        return env
+    return os.path.normpath(os.path.join(HERE, "..", "..", "reference"))
+
+
+def build(ref_root=None):
+    src = os.path.join(ref_root or _default_root(), "python", "modeling_big_bird.py")
     dst_dir = os.path.join(HERE, "_ref")
     if not os.path.exists(src):
         return None

@@ -76,6 +76,7 @@ _SIGS = {
     "rt_encoder_set_layer": (C.c_int, [_vp, C.c_int, C.c_uint32, C.c_int] + [_vp] * 12),
     "rt_encoder_set_embeddings": (C.c_int, [_vp] * 6),
     "rt_encoder_set_option": (C.c_int, [_vp, C.c_char_p, C.c_int]),
+    "rt_encoder_get_option": (C.c_int, [_vp, C.c_char_p, C.POINTER(C.c_int)]),
     "rt_encoder_prepare_batch": (C.c_int, [_vp, _i32p, C.c_int]),
     "rt_encoder_forward_hidden": (C.c_int, [_vp, _vp, C.c_int, C.c_int, _vp]),
     "rt_encoder_forward_ids": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp]),

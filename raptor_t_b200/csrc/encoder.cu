@@ -657,6 +657,16 @@ extern "C" rt_status rt_encoder_set_option(rt_encoder* e, const char* name, int 
   return fail(RT_ERR_INVALID, "set_option: unknown option '%s'", name);
 }
 
+extern "C" rt_status rt_encoder_get_option(rt_encoder* e, const char* name, int* value_out) {
+  RT_REQUIRE(e && name && value_out, RT_ERR_INVALID, "get_option: null pointer");
+  if (std::strcmp(name, "fuse_gelu") == 0) *value_out = e->fuse_gelu;
+  else if (std::strcmp(name, "fuse_qkv") == 0) *value_out = e->fuse_qkv;
+  else if (std::strcmp(name, "fuse_layernorm") == 0) *value_out = e->fuse_layernorm;
+  else if (std::strcmp(name, "fuse_residual") == 0) *value_out = e->fuse_residual;
+  else return fail(RT_ERR_INVALID, "get_option: unknown option '%s'", name);
+  return RT_OK;
+}
+
 extern "C" rt_status rt_encoder_prepare_batch(rt_encoder* e, const int32_t* lens, int n_seq) {
   RT_REQUIRE(e != nullptr, RT_ERR_INVALID, "prepare_batch: null encoder");
   RT_TRY(validate_lengths(e->cfg, lens, n_seq));

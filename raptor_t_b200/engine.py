@@ -61,6 +61,18 @@ class Encoder:
     def set_option(self, name, value):
         check(lib.rt_encoder_set_option(self._h, name.encode(), int(value)))
 
+    def get_option(self, name):
+        v = C.c_int()
+        check(lib.rt_encoder_get_option(self._h, name.encode(), C.byref(v)))
+        return int(v.value)
+
+    def layernorm_in_projection(self):
+        """Which of the two hidden-wide projections carry their LayerNorm in the current configuration:
+        (attention output, FFN down)."""
+        mode, H, F = self.get_option("fuse_layernorm"), self.cfg.hidden, self.cfg.ffn
+        both = mode == 2 and H in (768, 1024)
+        return both, both or (mode == 1 and H == 768 and F >= 2048)
+
     # ---- per batch -------------------------------------------------------------
     def prepare(self, lens_tokens):
         lens = np.ascontiguousarray(lens_tokens, dtype=np.int32)

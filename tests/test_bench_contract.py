@@ -44,7 +44,8 @@ def test_gpu_arm_line():
     d = _run(["--steps", "2", "--warmup", "3"], timeout=280)
     assert BASE_KEYS | {"roofline", "cpu_baseline", "gpu_launches", "clocks"} <= set(d)
     assert d["n_gpus"] == 1 and d["steps"] == 2 and d["warmup"] == 4 and d["value"] > 1e5  # 4 rotating batches
-    assert d["gpu_launches"] >= 2 * 80 and d["dtype"] == "f16" and d["data"] == "synthetic"
+    assert d["gpu_launches"] >= 2 * 70  # 6 kernels per layer + embeddings + position ids per step
+    assert d["dtype"] == "f16" and d["data"] == "synthetic"
     r = d["roofline"]
     assert r["bound"] == "tensor" and r["unit"] == "TFLOP/s" and 0 < r["frac"] < 1.2
     assert abs(r["frac"] - r["achieved"] / r["peak"]) < 1e-9
