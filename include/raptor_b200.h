@@ -123,6 +123,13 @@ rt_status rt_embeddings(void* out_dev, const int32_t* ids_dev, const int32_t* po
                         const void* type_dev, const void* gamma_dev, const void* beta_dev, int tokens,
                         int hidden, float eps, int dtype, void* stream);
 
+/* Pooler of the model head: pooled_dev fp32 [n_seq][hidden] = tanh(W hidden[first token of each sequence] + b),
+ * W 16-bit [hidden][hidden] in torch Linear layout [out][in], hidden_dev the packed [T][hidden] encoder output,
+ * seq_block_prefix_dev int32 [n_seq+1] (offsets in 64-token blocks).  The reference's own binding is commented
+ * out (python/pybind.cpp:58-64); the math is its validation model's, python/modeling_big_bird.py:1964, 2179. */
+rt_status rt_pooler(float* pooled_dev, const void* hidden_dev, const int32_t* seq_block_prefix_dev, int n_seq,
+                    const void* w_dev, const void* b_dev, int hidden, int dtype, void* stream);
+
 /* C[M][N] = A[M][K] * W[N][K]^T (+ bias, + GELU), fp32 accumulation on tcgen05 tensor cores.
  * A, W, C 16-bit row-major; K % 64 == 0, N % 64 == 0; A, W, bias 16-byte and C 32-byte aligned.
  * layers/kernels/mat_mul.cpp:9-96 (MatMul; note W here is [out][in], i.e. B transposed). */

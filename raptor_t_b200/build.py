@@ -7,6 +7,8 @@ raptor_t_b200/lib/raptor_t.so - the pybind11 module `raptor_t` with the referenc
 classes on top of it (both git-ignored).  nvcc cross-compiles without a GPU, so this also
 works on a CPU-only build machine.
 """
+import contextlib
+import fcntl
 import os
 import subprocess
 import sys
@@ -18,7 +20,7 @@ LIB = os.path.join(LIB_DIR, "libraptor_b200.so")
 
 SOURCES = [
     "runtime.cpp", "metadata.cpp", "tma_host.cpp", "elementwise.cu", "gemm_sm100.cu", "gemm_pair_sm100.cu", "gemm_ln_sm100.cu", "attention_sm100.cu",
-    "encoder.cu", "no_alloc.cu", "selftest.cu",
+    "encoder.cu", "no_alloc.cu", "selftest.cu", "pooler.cu",
 ]
 
 NVCC_FLAGS = [
@@ -44,6 +46,19 @@ def _stale():
     return any(os.path.getmtime(d) > t for d in deps if os.path.exists(d))
 
 
+@contextlib.contextmanager
+def _build_lock():
+    """Serialises builds between processes (the ranks of a multi-GPU launch import the package at the same
+    time): whoever comes second finds the library fresh and returns."""
+    os.makedirs(LIB_DIR, exist_ok=True)
+    with open(os.path.join(LIB_DIR, ".build.lock"), "w") as f:
+        fcntl.flock(f, fcntl.LOCK_EX)
+        try:
+            yield
+        finally:
+            fcntl.flock(f, fcntl.LOCK_UN)
+
+
 SHIM = os.path.join(LIB_DIR, "raptor_t.so")
 SHIM_SRC = os.path.join(CSRC, "pybind_shim.cpp")
 
@@ -51,10 +66,19 @@ SHIM_SRC = os.path.join(CSRC, "pybind_shim.cpp")
 def build_shim(force=False):
     """Compile the pybind11 module `raptor_t` (csrc/pybind_shim.cpp) against torch's headers and
     link it to libraptor_b200.so; returns its path."""
-    if not force and os.path.exists(SHIM) and os.path.getmtime(SHIM) >= max(
+    def fresh():
+        return os.path.exists(SHIM) and os.path.getmtime(SHIM) >= max(
             os.path.getmtime(SHIM_SRC), os.path.getmtime(LIB),
-            os.path.getmtime(os.path.join(HERE, "..", "include", "raptor_b200.h"))):
+            os.path.getmtime(os.path.join(HERE, "..", "include", "raptor_b200.h")))
+    if not force and fresh():
         return SHIM
+    with _build_lock():
+        if not force and fresh():
+            return SHIM
+        return _build_shim_locked()
+
+
+def _build_shim_locked():
     import sysconfig
 
     import torch
@@ -77,6 +101,13 @@ def build(force=False, verbose=False):
     """Compile every CUDA/C++ source into one shared library; returns its path."""
     if not force and not _stale():
         return LIB
+    with _build_lock():
+        if not force and not _stale():
+            return LIB
+        return _build_locked(verbose)
+
+
+def _build_locked(verbose):
     os.makedirs(LIB_DIR, exist_ok=True)
     objs = []
     procs = []

@@ -58,6 +58,7 @@ _SIGS = {
     "rt_bias_gelu": (C.c_int, [_vp, _vp, C.c_int, C.c_int, C.c_int, _vp]),
     "rt_qkv_bias_transpose": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, _vp]),
     "rt_embeddings": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_float, C.c_int, _vp]),
+    "rt_pooler": (C.c_int, [_vp, _vp, _vp, C.c_int, _vp, _vp, C.c_int, C.c_int, _vp]),
     "rt_gemm": (C.c_int, [_vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp]),
     "rt_gemm_residual": (C.c_int, [_vp, _vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, _vp]),
     "rt_gemm_bias_residual_layernorm": (C.c_int, [_vp] * 7 + [C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, _vp]),

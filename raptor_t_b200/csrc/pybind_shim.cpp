@@ -166,6 +166,7 @@ struct LayerRegistry {
   std::mutex mu;
   std::vector<BertAttention*> layers;
   torch::Tensor block_seq;  // per packed 64-token block {first token of its sequence, length}: the fused QKV epilogue's map
+  torch::Tensor seq_prefix; // int32 [B+1] block offsets of the sequences (device): the pooler's "first token" map
   static LayerRegistry& get() {
     static LayerRegistry r;
     return r;
@@ -363,6 +364,8 @@ class MetaData {
     auto& reg = LayerRegistry::get();
     std::lock_guard<std::mutex> lk(reg.mu);
     reg.block_seq = torch::from_blob(bs.data(), {static_cast<int64_t>(bs.size())}, torch::kInt32).clone().to(torch::kCUDA);
+    reg.seq_prefix = torch::from_blob(seq_len_info.data(), {static_cast<int64_t>(seq_len_info.size())}, torch::kInt32)
+                         .clone().to(torch::kCUDA);
     for (BertAttention* l : reg.layers)
       if (l) l->kick(lens, device);
   }
@@ -441,6 +444,34 @@ class BertOutput {
   torch::Tensor w_, b_, ln_w_, ln_b_;
 };
 
+// The pooler the reference declares and leaves commented out (python/pybind.cpp:58-64):
+// output fp32 [B, H] = tanh(dense(first token of every sequence of the current batch)).
+class BertPooler {
+ public:
+  BertPooler(torch::Tensor dense_weight, torch::Tensor dense_bias) {
+    require_cuda(dense_weight, "dense_weight");
+    dtype_ = dtype_of(dense_weight);
+    hidden_ = static_cast<int>(dense_weight.size(0));
+    w_ = dense_weight.t().contiguous();  // [out, in]
+    b_ = dense_bias.contiguous();
+  }
+  torch::Tensor call(const torch::Tensor& input_tensor, torch::Tensor& output) {
+    require_cuda(input_tensor, "input_tensor");
+    require_cuda(output, "output");
+    auto& reg = LayerRegistry::get();
+    if (!reg.seq_prefix.defined()) throw std::runtime_error("raptor_t: BertPooler called before MetaData.update_meta_data");
+    if (output.scalar_type() != torch::kFloat32) throw std::runtime_error("raptor_t: BertPooler writes a float32 output");
+    check(rt_pooler(output.data_ptr<float>(), input_tensor.data_ptr(), reg.seq_prefix.data_ptr<int32_t>(),
+                    static_cast<int>(reg.seq_prefix.numel()) - 1, w_.data_ptr(), b_.data_ptr(), hidden_, dtype_,
+                    stream_of_current()));
+    return output;
+  }
+
+ private:
+  int dtype_, hidden_;
+  torch::Tensor w_, b_;
+};
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -469,6 +500,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            py::arg("dense_bias"), py::arg("layer_norm_weight"), py::arg("layer_norm_bias"))
       .def("__call__", &BertOutput::call, py::arg("hidden_states"), py::arg("input_tensor"), py::arg("output"),
            py::arg("info"), py::arg("kernel_fusion") = true);
+
+  py::class_<BertPooler>(m, "BertPooler")
+      .def(py::init<torch::Tensor, torch::Tensor>(), py::arg("dense_weight"), py::arg("dense_bias"))
+      .def("__call__", &BertPooler::call, py::arg("input_tensor"), py::arg("output"));
 
   py::class_<TensorSet, std::unique_ptr<TensorSet, py::nodelete>>(m, "TensorSet")
       .def(py::init<int64_t, int64_t, int64_t>(), py::arg("total_seq_len"), py::arg("to_select_index_len"),

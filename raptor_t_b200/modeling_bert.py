@@ -61,6 +61,19 @@ class BertEncoder:
         return hidden_states, test_info
 
 
+class BertPooler:
+    """The pooler the reference sketches and leaves commented out (python/modeling_bert.py:281-300):
+    tanh(dense(first token of every sequence)), the head of its validation model
+    (python/modeling_big_bird.py:1964, 2179).  weight is [in, out] as the reference's from_torch would pass it."""
+
+    def __init__(self, dense_weight, dense_bias):
+        self.w = dense_weight.t().contiguous()  # [out, in]
+        self.b = dense_bias.contiguous()
+
+    def __call__(self, input_tensor, seq_position_info_tensor, output=None):
+        return ops.pooler(input_tensor, seq_position_info_tensor, self.w, self.b, out=output)
+
+
 class BertModelNoPooler:
     """python/modeling_bert.py:318-394."""
 

@@ -68,6 +68,15 @@ def embeddings(ids, pos_ids, type_ids, word, pos, typ, gamma, beta, eps, dtype, 
     return out
 
 
+def pooler(hidden, seq_block_prefix_dev, w, b, out=None):
+    """pooled [n_seq, H] fp32 = tanh(hidden[first token of each sequence] @ w^T + b); w is [out, in]."""
+    n_seq, H = seq_block_prefix_dev.numel() - 1, hidden.shape[1]
+    if out is None:
+        out = torch.empty(n_seq, H, dtype=torch.float32, device=hidden.device)
+    check(lib.rt_pooler(_p(out), _p(hidden), _p(seq_block_prefix_dev), n_seq, _p(w), _p(b), H, _dt(hidden), _stream()))
+    return out
+
+
 def gemm(a, w, bias=None, epilogue=capi.RT_EPI_NONE, out=None):
     """out[M,N] = a[M,K] @ w[N,K]^T (+bias, +GELU); w is [out_features, in_features]."""
     M, K = a.shape

@@ -12,6 +12,11 @@ from oracle import EncoderConfig
 pytestmark = pytest.mark.gpu
 
 MAX_ABS, MEAN_ABS = 2e-2, 2e-3
+# bf16 keeps 8 significant bits in every activation that crosses HBM (3 fewer than fp16) and does not meet
+# that bound; measured on a B200: 0.046 / 0.0032 on the 2-layer hidden-128 model, 0.07 / 0.007 at 12 layers.
+# The bf16 assertions below are those measurements plus a margin; every test prints what it measured.
+BF16_SMALL = (6e-2, 6e-3)
+BF16_BASE = (8e-2, 8e-3)
 
 
 def _make(cfg, dtype, P):
@@ -48,7 +53,9 @@ def test_small_encoder_from_ids(dtype, fuse):
     from raptor_t_b200 import ops
     ops.check_device()
     err = (out.float().cpu() - ref).abs()
-    assert err.max().item() < 6e-2 and err.mean().item() < 6e-3, (err.max().item(), err.mean().item())
+    print(f"PARITY small_encoder[{dtype}, fuse={fuse}] max_abs={err.max().item():.5f} mean_abs={err.mean().item():.6f}")
+    mx, mean = (MAX_ABS, MEAN_ABS) if dtype == torch.float16 else BF16_SMALL
+    assert err.max().item() < mx and err.mean().item() < mean, (err.max().item(), err.mean().item())
     # tables bit-exact with the oracle
     for layer in range(cfg.layers):
         ptr, idx = enc.table(layer)
@@ -69,10 +76,9 @@ def test_base_encoder_hidden_states_within_tolerance():
         enc.prepare(lens)
         out = enc.forward_ids(torch.cat(seqs).cuda())
         err = (out.float().cpu() - ref).abs()
-        if dtype == torch.float16:
-            assert err.max().item() < MAX_ABS and err.mean().item() < MEAN_ABS, (err.max().item(), err.mean().item())
-        else:  # bf16 carries 3 fewer mantissa bits through the residual stream
-            assert err.max().item() < 8e-2 and err.mean().item() < 8e-3, (err.max().item(), err.mean().item())
+        print(f"PARITY base_3_layers[{dtype}] max_abs={err.max().item():.5f} mean_abs={err.mean().item():.6f}")
+        mx, mean = (MAX_ABS, MEAN_ABS) if dtype == torch.float16 else BF16_BASE
+        assert err.max().item() < mx and err.mean().item() < mean, (err.max().item(), err.mean().item())
         enc.close()
 
 
@@ -117,7 +123,8 @@ def test_large_shape_layers_within_tolerance():
     from raptor_t_b200 import ops
     ops.check_device()
     err = (out.float().cpu() - ref).abs()
-    assert err.max().item() < 8e-2 and err.mean().item() < 8e-3, (err.max().item(), err.mean().item())
+    print(f"PARITY large_dims_2_layers[bf16] max_abs={err.max().item():.5f} mean_abs={err.mean().item():.6f}")
+    assert err.max().item() < BF16_BASE[0] and err.mean().item() < BF16_BASE[1], (err.max().item(), err.mean().item())
     for layer in range(cfg.layers):
         ptr, idx = enc.table(layer)
         optr, oidx = oracle.build_block_csr(lens, cfg, layer)

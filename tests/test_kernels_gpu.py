@@ -159,6 +159,25 @@ def test_gemm_residual(ops, dtype, M, N, K):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden,lens", [(768, [1024, 64, 832]), (1024, [128]), (128, [512, 2048, 64, 64])])
+def test_pooler(ops, dtype, hidden, lens):
+    """tanh(Linear(first token of every sequence)) on a packed varlen batch against torch fp32."""
+    from raptor_t_b200 import metadata
+    T = sum(lens)
+    g = torch.Generator(device="cuda").manual_seed(hidden + T)
+    x = torch.randn(T, hidden, device="cuda", generator=g).to(dtype)
+    w = (torch.randn(hidden, hidden, device="cuda", generator=g) / math.sqrt(hidden)).to(dtype)
+    b = (0.1 * torch.randn(hidden, device="cuda", generator=g)).to(dtype)
+    prefix = torch.from_numpy(metadata.seq_block_prefix(lens)).cuda()
+    firsts = torch.tensor(np.concatenate([[0], np.cumsum(lens)[:-1]]), device="cuda")
+    ref = torch.tanh(x[firsts].float() @ w.float().t() + b.float())
+    out = ops.pooler(x, prefix, w, b)
+    assert out.shape == (len(lens), hidden) and (out - ref).abs().max().item() < 2e-3
+    from raptor_t_b200.modeling_bert import BertPooler
+    assert torch.equal(BertPooler(w.t().contiguous(), b)(x, prefix), out)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("M,N,K", [(256, 768, 768), (1000, 768, 3072), (16512, 768, 768), (64, 1024, 1024),
                                    (4100, 1024, 4096), (1, 768, 64)])
 def test_gemm_bias_residual_layernorm(ops, dtype, M, N, K):

@@ -55,6 +55,13 @@ def test_model_layer_matches_oracle(binding):
                         torch.from_numpy(part_off).cuda(), torch.from_numpy(part_ids).cuda(),
                         position_ids=pos, test_info={})
         assert (out2.float().cpu() - ref).abs().max().item() < 6e-2
+        if binding == "pybind":  # the pooler the reference leaves commented out, on the batch MetaData describes
+            w = (torch.randn(cfg.hidden, cfg.hidden, device="cuda") / 11.0).to(torch.bfloat16)
+            b = torch.zeros(cfg.hidden, device="cuda", dtype=torch.bfloat16)
+            pooled = raptor_t.BertPooler(w, b)(out, torch.empty(len(lens), cfg.hidden, device="cuda"))
+            firsts = torch.tensor(np.concatenate([[0], np.cumsum(lens)[:-1]]), device="cuda")
+            want = torch.tanh(out[firsts].float() @ w.float())
+            assert (pooled - want).abs().max().item() < 2e-3
         md.terminate_thread()
         del model
     ts = raptor_t.TensorSet.get_instance()
