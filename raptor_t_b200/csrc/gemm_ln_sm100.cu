@@ -369,7 +369,6 @@ rt_status launch_ln(void* out, const void* a, const void* w, const void* bias, c
     int n = 0;
     if (cudaOccupancyMaxActiveClusters(&n, kern, &q) != cudaSuccess || n <= 0) n = gemm_sm_count() / (2 * NT);
     resident[dev] = n;
-    if (getenv("RAPTOR_DEBUG_CLUSTERS")) fprintf(stderr, "gemm_ln: NT=%d resident clusters=%d\n", NT, n);
   }
   const int clusters = std::max(1, std::min(m_tiles, resident[dev]));
   cudaLaunchConfig_t cfg{};
