@@ -12,12 +12,15 @@
 //            operand.  The only role that reads the work list in global memory (4-byte
 //            asynchronous copies, eight entries ahead); it publishes one record per step
 //            ({entries, first/last flags, key/value rows}) in a shared-memory ring.
-//   warp 5   MMA issuer (one thread): S = Q K^T as M=128 N=128 K=64 (both operands K-major in
-//            shared memory) into the score columns of TMEM, and O += P V (P read from TMEM,
-//            V MN-major in shared memory) into the output columns.  The scores of step g+1
-//            are issued as soon as the softmax warps have pulled step g's scores into
-//            registers, i.e. under their exponentials; the PV product of a step is issued in
-//            two halves, each as soon as that half of the probabilities has been stored.
+//   warp 5   MMA issuer, scores: S = Q K^T as M=128 N=128 K=64 (both operands K-major in
+//            shared memory) into the score columns of TMEM.  The scores of step g+1 are
+//            issued as soon as the softmax warps have pulled step g's scores into registers,
+//            i.e. under their exponentials.
+//   warp 6   MMA issuer, outputs: O += P V (P read from TMEM, V MN-major in shared memory) into
+//            the output columns, in two halves per step, each as soon as that half of the
+//            probabilities has been stored.  (tcgen05.mma blocks its issuing thread while the
+//            tensor pipe's queue is full: with one issuing warp the output MMAs of a step sat
+//            behind the score MMAs of the next.)
 //   warps 0-3  softmax: thread r owns tile row r (TMEM lane r).  It pulls its score row out of
 //            TMEM, keeps the running max / sum in fp32 (base-2 exponentials) and writes the
 //            16-bit probabilities to their own TMEM columns.  The output tile accumulates in
@@ -25,7 +28,8 @@
 //            more than 2^8 since the last rescale ("lazy" rescaling: probabilities are then at
 //            most 256, well inside 16-bit range), and read once per item for the final
 //            division by the row sum.  Warps whose query block does not use an entry skip its
-//            exponentials and keep zeros in its probability columns.
+//            exponentials and keep zeros in its probability columns.  Every fourth pair of
+//            exponentials is a cubic on the FMA pipe instead of the exponential unit.
 // The kernel is launched with 128 registers per thread; the upper warpgroup hands registers
 // to the softmax warps (setmaxnreg), which hold a 128-column score row each.
 //
@@ -60,7 +64,7 @@ namespace {
 
 using namespace ptx;
 
-constexpr int kThreads = 256;            // warps 0-3 softmax; 4: loader, 5: MMA issue (one thread each); 6-7 only lend registers
+constexpr int kThreads = 256;            // warps 0-3 softmax; 4: loader, 5: score MMAs, 6: output MMAs; 7 only lends registers
 constexpr int kStagesK = 2;              // K ring depth in steps (a slot is free again once the S MMA has read it)
 constexpr int kStagesV = 3;              // V ring depth in steps (a slot is held until the PV MMA, a softmax period later)
 constexpr int kStepRing = 16;            // per-step records travel from the loader to the other roles through smem
@@ -163,7 +167,30 @@ __device__ __forceinline__ float max64(const uint32_t* s) {
   return fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
 }
 
+// 2^x for a pair of arguments on the FMA pipe (the exponential unit is the kernel's bottleneck, a part of
+// the columns goes here instead): clamp, split x = n + f with |f| <= 0.5 by adding 1.5 * 2^23 (the integer
+// lands in the low mantissa bits), 2^f by a cubic (relative error 7.5e-5, below the 16-bit rounding of the
+// probabilities), n added to the exponent field.
+__device__ __forceinline__ void ex2_fma_pair(float x0, float x1, float& r0, float& r1) {
+  x0 = fmaxf(x0, -126.f);
+  x1 = fmaxf(x1, -126.f);
+  const unsigned long long x = f2_pack(x0, x1);
+  const unsigned long long xr = f2_add(x, f2_pack(12582912.f, 12582912.f));
+  const unsigned long long n = f2_add(xr, f2_pack(-12582912.f, -12582912.f));
+  const unsigned long long f = f2_fma(n, f2_pack(-1.f, -1.f), x);
+  unsigned long long r = f2_fma(f, f2_pack(0.05517167f, 0.05517167f), f2_pack(0.24261112f, 0.24261112f));
+  r = f2_fma(r, f, f2_pack(0.69326099f, 0.69326099f));
+  r = f2_fma(r, f, f2_pack(0.99992807f, 0.99992807f));
+  float a0, a1, b0, b1;
+  f2_unpack(r, a0, a1);
+  f2_unpack(xr, b0, b1);
+  r0 = __int_as_float(__float_as_int(a0) + (__float_as_int(b0) << 23));
+  r1 = __int_as_float(__float_as_int(a1) + (__float_as_int(b1) << 23));
+}
+
 // p[i] = 2^(s[2i] * c - m), 2^(s[2i+1] * c - m) packed to 16 bits, for 64 scores; returns their sum.
+// Every kPolyEvery-th pair is computed on the FMA pipe.
+constexpr int kPolyEvery = 4;  // measured: 3 and 4 are equal within noise, 2 is slower (issue slots)
 template <bool BF16>
 __device__ __forceinline__ float exp64(const uint32_t* s, uint32_t* p, float scale_log2, float m_ref) {
   const unsigned long long c2 = f2_pack(scale_log2, scale_log2);
@@ -174,7 +201,13 @@ __device__ __forceinline__ float exp64(const uint32_t* s, uint32_t* p, float sca
     const unsigned long long t = f2_fma(f2_pack(__uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1])), c2, nm2);
     float t0, t1;
     f2_unpack(t, t0, t1);
-    const float p0 = ex2(t0), p1 = ex2(t1);
+    float p0, p1;
+    if (kPolyEvery > 0 && i % kPolyEvery == kPolyEvery - 1) {
+      ex2_fma_pair(t0, t1, p0, p1);
+    } else {
+      p0 = ex2(t0);
+      p1 = ex2(t1);
+    }
     if (i & 1) acc1 = f2_add(acc1, f2_pack(p0, p1));
     else acc0 = f2_add(acc0, f2_pack(p0, p1));
     p[i] = pack2<BF16>(p0, p1);
@@ -315,30 +348,31 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         cp_async_wait<0>();
       }
     } else if (warp == 5) {
-      // ------------------------------------------------------------------ MMA issuer
+      // ------------------------------------------------------------------ MMA issuer, scores
       // The whole warp walks the loop (waits included) and one elected lane issues the MMAs and
       // commits: loop state and descriptors are then warp-uniform values, which the tensor-core
-      // instructions take directly.  Inside a single-lane branch every descriptor would have to be
-      // moved over from a per-thread register first, and that serial latency (a dozen MMAs per
-      // step) paced the pipeline.
+      // instructions take directly.  Scores and outputs have an issuing warp each: tcgen05.mma
+      // blocks while the tensor pipe's queue is full, and one warp issuing both kinds held the
+      // output MMAs of step g behind the score MMAs of step g+1 (and the reverse).
       if (item_begin < item_end) {
         const bool leader = elect_one();
         constexpr uint32_t idesc_s128 = make_idesc_f16(128, 128, BF16 ? 1 : 0, false);
         constexpr uint32_t idesc_s64 = make_idesc_f16(128, 64, BF16 ? 1 : 0, false);
-        constexpr uint32_t idesc_pv = make_idesc_f16(128, 64, BF16 ? 1 : 0, true);
         uint32_t total_steps = 0;
         for (int idx = item_begin; idx < item_end; ++idx) total_steps += steps_of(items[idx].n_entries);
-        uint32_t s_itn = 0, pv_itn = 0;
-        bool ok = true;
-        const uint32_t q_addr = smem_u32(sm.q[0]), k_addr = smem_u32(sm.k[0]), v_addr = smem_u32(sm.v[0]);
-        // S = Q K^T of step g into the score columns (free: the softmax warps hold step g-1's scores in registers)
-        auto issue_s = [&](uint32_t g) -> bool {
+        uint32_t s_itn = 0;
+        const uint32_t q_addr = smem_u32(sm.q[0]), k_addr = smem_u32(sm.k[0]);
+        for (uint32_t g = 0; g < total_steps; ++g) {
+          // S = Q K^T of step g into the score columns, free once the softmax warps hold step g-1's scores
+          if (g > 0) {
+            if (!mbar_wait(&sm.s_free, (g - 1) & 1, ab, 220)) break;
+          }
           const int sk = g % kStagesK;
-          if (!mbar_wait(&sm.k_full[sk], (g / kStagesK) & 1, ab, 218)) return false;
+          if (!mbar_wait(&sm.k_full[sk], (g / kStagesK) & 1, ab, 218)) break;
           const int4 rec = sm.step_ring[g % kStepRing];
           const int qb = s_itn & 1;
           if (rec.x & kRecFirst) {
-            if (!mbar_wait(&sm.q_full[qb], (s_itn >> 1) & 1, ab, 219)) return false;
+            if (!mbar_wait(&sm.q_full[qb], (s_itn >> 1) & 1, ab, 219)) break;
           }
           tc_fence_after_sync();
           const uint64_t dq = make_smem_desc_sw128(q_addr + qb * kStepBytes);
@@ -358,17 +392,22 @@ sparse_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           }
           if (rec.x & kRecLast) ++s_itn;
           __syncwarp();
-          return true;
-        };
-        ok = total_steps == 0 || issue_s(0);
-        for (uint32_t g = 0; ok && g < total_steps; ++g) {
-          const int4 rec = sm.step_ring[g % kStepRing];
-          if (g + 1 < total_steps) {
-            if (!mbar_wait(&sm.s_free, g & 1, ab, 220)) break;  // step g's scores are in registers
-            if (!issue_s(g + 1)) break;
-          }
+        }
+      }
+    } else if (warp == 6) {
+      // ------------------------------------------------------------------ MMA issuer, outputs
+      if (item_begin < item_end) {
+        const bool leader = elect_one();
+        constexpr uint32_t idesc_pv = make_idesc_f16(128, 64, BF16 ? 1 : 0, true);
+        uint32_t total_steps = 0;
+        for (int idx = item_begin; idx < item_end; ++idx) total_steps += steps_of(items[idx].n_entries);
+        uint32_t pv_itn = 0;
+        const uint32_t v_addr = smem_u32(sm.v[0]);
+        for (uint32_t g = 0; g < total_steps; ++g) {
           const int sv = g % kStagesV;
+          // the loader published the step's record before it armed the key barrier, and arms this one later
           if (!mbar_wait(&sm.v_full[sv], (g / kStagesV) & 1, ab, 214)) break;
+          const int4 rec = sm.step_ring[g % kStepRing];
           const bool first = (rec.x & kRecFirst) != 0;
           if (first) {
             // the output tile is overwritten: the softmax warps must have read the previous item's result
