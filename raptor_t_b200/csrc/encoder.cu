@@ -174,16 +174,17 @@ struct rt_encoder {
   cudaStream_t meta_stream = nullptr;
 
   // Host-buffer pipeline (rt_encoder_submit_host / rt_encoder_wait_host): batches run back
-  // to back on pipe_stream, each into its own device output buffer, and copy_stream carries
-  // a finished batch to the caller's memory while the next batch computes.
+  // to back on pipe_stream, each with its own device id and output buffers; in_stream brings a
+  // batch's ids over while the previous batch computes, and copy_stream carries a finished
+  // batch to the caller's memory while the next batch computes.
   struct HostJob {
-    DevBuf out;
-    cudaEvent_t computed = nullptr, copied = nullptr;
+    DevBuf ids, out;
+    cudaEvent_t ids_ready = nullptr, computed = nullptr, copied = nullptr;
     int* err_host = nullptr;  // pinned copy of the device error word, taken behind the output copy
     bool busy = false;
     uint64_t ticket = 0;
   } jobs[2];
-  cudaStream_t pipe_stream = nullptr, copy_stream = nullptr;
+  cudaStream_t pipe_stream = nullptr, copy_stream = nullptr, in_stream = nullptr;
   uint64_t next_ticket = 1;
   // persistent metadata worker: sleeps on `cv` until prepare_batch posts a job
   std::thread worker;
@@ -579,13 +580,16 @@ extern "C" rt_status rt_encoder_destroy(rt_encoder* e) {
   }
   for (auto& ev : e->timer.pool) cudaEventDestroy(ev);
   for (auto& job : e->jobs) {
+    job.ids.release();
     job.out.release();
+    if (job.ids_ready) cudaEventDestroy(job.ids_ready);
     if (job.computed) cudaEventDestroy(job.computed);
     if (job.copied) cudaEventDestroy(job.copied);
     if (job.err_host) cudaFreeHost(job.err_host);
   }
   if (e->pipe_stream) cudaStreamDestroy(e->pipe_stream);
   if (e->copy_stream) cudaStreamDestroy(e->copy_stream);
+  if (e->in_stream) cudaStreamDestroy(e->in_stream);
   if (e->meta_stream) cudaStreamDestroy(e->meta_stream);
   delete e;
   return RT_OK;
@@ -841,7 +845,9 @@ extern "C" rt_status rt_encoder_submit_host(rt_encoder* e, const int32_t* lens, 
   if (!e->pipe_stream) {
     RT_CHECK_CUDA(cudaStreamCreateWithFlags(&e->pipe_stream, cudaStreamNonBlocking));
     RT_CHECK_CUDA(cudaStreamCreateWithFlags(&e->copy_stream, cudaStreamNonBlocking));
+    RT_CHECK_CUDA(cudaStreamCreateWithFlags(&e->in_stream, cudaStreamNonBlocking));
     for (auto& job : e->jobs) {
+      RT_CHECK_CUDA(cudaEventCreateWithFlags(&job.ids_ready, cudaEventDisableTiming));
       RT_CHECK_CUDA(cudaEventCreateWithFlags(&job.computed, cudaEventDisableTiming));
       RT_CHECK_CUDA(cudaEventCreateWithFlags(&job.copied, cudaEventDisableTiming));
       RT_CHECK_CUDA(cudaMallocHost(&job.err_host, sizeof(int)));
@@ -860,12 +866,15 @@ extern "C" rt_status rt_encoder_submit_host(rt_encoder* e, const int32_t* lens, 
   RT_TRY(rt_encoder_prepare_batch(e, lens, n_seq));
   if (prev && prev->forward_recorded) RT_CHECK_CUDA(cudaStreamWaitEvent(e->pipe_stream, prev->forward_done, 0));
   const size_t T = e->tokens;
-  RT_TRY(e->ids_dev.ensure(T * sizeof(int32_t)));
+  RT_TRY(job.ids.ensure(T * sizeof(int32_t)));
   const size_t out_bytes = T * e->cfg.hidden * 2;
   RT_TRY(job.out.ensure(out_bytes));
   cudaStream_t st = e->pipe_stream;
-  RT_CHECK_CUDA(cudaMemcpyAsync(e->ids_dev.p, ids_host, T * sizeof(int32_t), cudaMemcpyHostToDevice, st));
-  RT_TRY(rt_encoder_forward_ids(e, (const int32_t*)e->ids_dev.p, nullptr, nullptr, job.out.p, st));
+  // this buffer's previous batch has reached the host (waited for above), so its ids are long consumed
+  RT_CHECK_CUDA(cudaMemcpyAsync(job.ids.p, ids_host, T * sizeof(int32_t), cudaMemcpyHostToDevice, e->in_stream));
+  RT_CHECK_CUDA(cudaEventRecord(job.ids_ready, e->in_stream));
+  RT_CHECK_CUDA(cudaStreamWaitEvent(st, job.ids_ready, 0));
+  RT_TRY(rt_encoder_forward_ids(e, (const int32_t*)job.ids.p, nullptr, nullptr, job.out.p, st));
   RT_CHECK_CUDA(cudaEventRecord(job.computed, st));
   RT_CHECK_CUDA(cudaStreamWaitEvent(e->copy_stream, job.computed, 0));
   RT_CHECK_CUDA(cudaMemcpyAsync(out_host, job.out.p, out_bytes, cudaMemcpyDeviceToHost, e->copy_stream));
