@@ -204,7 +204,7 @@ def test_gemm_bias_residual_layernorm(ops, dtype, M, N, K):
     ops.check_device()
 
 
-def _attention_case(ops, dtype, cfg, lens, layer, seed):
+def _attention_case(ops, dtype, cfg, lens, layer, seed, key_ramp=0.0):
     from raptor_t_b200 import capi, metadata
     rc = capi.make_config(hidden=cfg.hidden, heads=cfg.heads, ffn=cfg.ffn, layers=cfg.layers, max_pos=cfg.max_pos,
                           pattern=cfg.pattern, band_half=cfg.band_half,
@@ -219,7 +219,15 @@ def _attention_case(ops, dtype, cfg, lens, layer, seed):
     v = torch.empty(T * H, dtype=dtype)
     refs, t0 = [], 0
     for n in lens:
-        qs, ks, vs = (torch.randn(nh, n, 64, generator=g).to(dtype) for _ in range(3))
+        qs, ks, vs = (torch.randn(nh, n, 64, generator=g) for _ in range(3))
+        if key_ramp != 0.0:
+            # scores that climb (or fall) by 64 * |key_ramp| per key block, i.e. by more than 2^8 from one block to the
+            # next: whatever order a list is walked in, the running maximum keeps moving and the accumulated output
+            # has to be rescaled again and again
+            blk = (torch.arange(n) // 64).float().view(1, n, 1)
+            qs = 1.0 + 0.1 * qs
+            ks = key_ramp * blk + 0.1 * ks
+        qs, ks, vs = qs.to(dtype), ks.to(dtype), vs.to(dtype)
         for buf, src in ((q, qs), (k, ks), (v, vs)):
             buf[t0 * H:(t0 + n) * H] = src.reshape(-1)
         L = n // 64
@@ -250,6 +258,13 @@ def test_sparse_attention_bigbird(ops, dtype, lens):
 def test_sparse_attention_12_heads_layer_seed(ops):
     cfg = EncoderConfig()
     _attention_case(ops, torch.bfloat16, cfg, [1024, 1856], layer=7, seed=3)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("key_ramp", [0.75, -0.75])
+def test_sparse_attention_moving_maximum(ops, dtype, key_ramp):
+    cfg = EncoderConfig(hidden=128, heads=2, ffn=256, layers=1)
+    _attention_case(ops, dtype, cfg, [1024, 2112], layer=0, seed=5, key_ramp=key_ramp)
 
 
 @pytest.mark.parametrize("lens", [[1280], [512, 64, 2048]])
