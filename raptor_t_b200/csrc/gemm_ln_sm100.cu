@@ -179,9 +179,12 @@ gemm_ln_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer (pair leaders)
-    if (lane == 0 && hrow == 0) {
+    // the whole warp walks the loop, one elected lane issues (see gemm_pair_sm100.cu)
+    if (hrow == 0) {
       constexpr uint32_t idesc = make_idesc_f16(kTileM, kTileN, BF16 ? 1 : 0, false);
       const uint16_t pair_mask = static_cast<uint16_t>(3u << leader);
+      const bool elected = elect_one();
+      const uint32_t smem_base = smem_u32(smem);
       uint32_t it = 0, tile_it = 0;
       bool ok = true;
       for (int t = cluster_id; t < n_tiles_m && ok; t += n_clusters, ++tile_it) {
@@ -195,15 +198,19 @@ gemm_ln_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const uint32_t ph = (it / kStages) & 1;
           if (!mbar_wait(&full[s], ph, ab, 123)) { ok = false; break; }
           tc_fence_after_sync();
-          const uint32_t sa = smem_u32(smem + s * kStageBytes);
+          const uint32_t sa = smem_base + s * kStageBytes;
           const uint64_t da = make_smem_desc_sw128(sa);
           const uint64_t db = make_smem_desc_sw128(sa + kABytes);
+          if (elected) {
 #pragma unroll
-          for (int k = 0; k < kBK / 16; ++k)
-            mma_ss_pair(d_tmem, da + (k * 32 >> 4), db + (k * 32 >> 4), idesc, (kb | k) ? 1u : 0u);
-          tc_commit_pair(&empty[s], pair_mask);  // slot free in both CTAs of the pair
+            for (int k = 0; k < kBK / 16; ++k)
+              mma_ss_pair(d_tmem, da + (k * 32 >> 4), db + (k * 32 >> 4), idesc, (kb | k) ? 1u : 0u);
+            tc_commit_pair(&empty[s], pair_mask);  // slot free in both CTAs of the pair
+          }
+          __syncwarp();
         }
-        if (ok) tc_commit_pair(&acc_full[a], pair_mask);
+        if (ok && elected) tc_commit_pair(&acc_full[a], pair_mask);
+        __syncwarp();
       }
     }
   } else {

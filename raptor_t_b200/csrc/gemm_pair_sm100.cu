@@ -113,8 +113,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer (leader CTA)
-    if (lane == 0 && rank == 0) {
+    // The whole warp walks the loop and one elected lane issues: descriptors and loop state are then
+    // warp-uniform values, which the tensor-core instructions take directly (inside a single-lane branch
+    // every descriptor is moved over from a per-thread register first, and that serial latency per
+    // 64-wide K slice is of the order of the slice's 512 clocks of MMA work).
+    if (rank == 0) {
       constexpr uint32_t idesc = make_idesc_f16(kTileM, kTileN, BF16 ? 1 : 0, false);
+      const bool leader = elect_one();
+      const uint32_t smem_base = smem_u32(smem);
       uint32_t it = 0, tile_it = 0;
       bool ok = true;
       for (int t = pair; t < n_tiles && ok; t += n_pairs, ++tile_it) {
@@ -128,15 +134,19 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           const uint32_t ph = (it / kStages) & 1;
           if (!mbar_wait(&full[s], ph, ab, 113)) { ok = false; break; }
           tc_fence_after_sync();
-          const uint32_t sa = smem_u32(smem + s * kStageBytes);
+          const uint32_t sa = smem_base + s * kStageBytes;
           const uint64_t da = make_smem_desc_sw128(sa);
           const uint64_t db = make_smem_desc_sw128(sa + kABytes);
+          if (leader) {
 #pragma unroll
-          for (int k = 0; k < kBK / 16; ++k)
-            mma_ss_pair(d_tmem, da + (k * 32 >> 4), db + (k * 32 >> 4), idesc, (kb | k) ? 1u : 0u);
-          tc_commit_pair(&empty[s], 3);  // slot free in both CTAs
+            for (int k = 0; k < kBK / 16; ++k)
+              mma_ss_pair(d_tmem, da + (k * 32 >> 4), db + (k * 32 >> 4), idesc, (kb | k) ? 1u : 0u);
+            tc_commit_pair(&empty[s], 3);  // slot free in both CTAs
+          }
+          __syncwarp();
         }
-        if (ok) tc_commit_pair(&acc_full[a], 3);
+        if (ok && leader) tc_commit_pair(&acc_full[a], 3);
+        __syncwarp();
       }
     }
   } else {

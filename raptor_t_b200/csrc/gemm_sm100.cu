@@ -132,8 +132,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    // the whole warp walks the loop, one elected lane issues (see gemm_pair_sm100.cu)
+    {
       constexpr uint32_t idesc = make_idesc_f16(kBM, BN, BF16 ? 1 : 0, false);
+      const bool elected = elect_one();
+      const uint32_t smem_base = smem_u32(smem);
       uint32_t it = 0, tile_it = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++tile_it) {
@@ -147,15 +150,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           const uint32_t ph = (it / Cfg::kStages) & 1;
           if (!mbar_wait(&full[s], ph, ab, 103)) { ok = false; break; }
           tc_fence_after_sync();
-          const uint32_t sa = smem_u32(smem + s * Cfg::kStageBytes);
+          const uint32_t sa = smem_base + s * Cfg::kStageBytes;
           const uint64_t da = make_smem_desc_sw128(sa);
           const uint64_t db = make_smem_desc_sw128(sa + Cfg::kABytes);
+          if (elected) {
 #pragma unroll
-          for (int k = 0; k < kBK / 16; ++k)
-            mma_ss(d_tmem, da + (k * 32 >> 4), db + (k * 32 >> 4), idesc, (kb | k) ? 1u : 0u);
-          tc_commit(&empty[s]);
+            for (int k = 0; k < kBK / 16; ++k)
+              mma_ss(d_tmem, da + (k * 32 >> 4), db + (k * 32 >> 4), idesc, (kb | k) ? 1u : 0u);
+            tc_commit(&empty[s]);
+          }
+          __syncwarp();
         }
-        if (ok) tc_commit(&acc_full[a]);
+        if (ok && elected) tc_commit(&acc_full[a]);
+        __syncwarp();
       }
     }
   } else {
