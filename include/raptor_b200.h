@@ -262,8 +262,9 @@ rt_status rt_encoder_forward_ids(rt_encoder* enc, const int32_t* ids_dev, const 
 rt_status rt_encoder_forward_host(rt_encoder* enc, const int32_t* lens_tokens, int n_seq,
                                   const int32_t* ids_host, void* out_host);
 /* The same in two halves, so that a caller keeps two batches in flight: submit enqueues
- * prepare_batch + H2D + forward on the encoder's own stream and the D2H of the result on a
- * second stream (the copy of batch i overlaps the kernels of batch i+1) and returns at once
+ * prepare_batch + forward on the encoder's own stream, the H2D of the ids on a second stream
+ * (into a per-batch buffer, under the previous batch's kernels) and the D2H of the result on a
+ * third (the copy of batch i overlaps the kernels of batch i+1) and returns at once
  * with a ticket; wait blocks until that batch's output is in out_host.  ids_host and out_host
  * belong to the library between the two calls (pinned memory, or the copies block).  A third
  * submit first waits for the oldest batch.  rt_encoder_forward_host == submit + wait.
