@@ -219,7 +219,8 @@ class Batch:
         self.T_local, self.T_total = int(sum(self.lens)), int(sum(self.lens_all))
         self.ids_dev = torch.from_numpy(ids_np).cuda()
         self.ids_pinned = torch.from_numpy(ids_np).pin_memory()
-        self.gatherer = (parallel.RootGatherer(self.assignment, self.lens_all, w["hidden"], dtype, "cuda", depth=DEPTH)
+        self.gatherer = (parallel.make_root_gatherer(self.assignment, self.lens_all, w["hidden"], dtype, "cuda", depth=DEPTH,
+                                                     kind=w.get("gather"))
                          if n_gpus > 1 else None)
 
 
@@ -486,7 +487,8 @@ def run_gpu(args, w):
                    "l2": "flushed between timed steps (256 MiB write)",
                    "stage_timing": "per-kernel durations (roofline, stages_ms_per_step) come from a second pass of the "
                                    "same steps with CUDA events around every launch",
-                   "parallelism": f"replicas x{n_gpus}, whole-sequence bin packing, gather of outputs to rank 0 timed (the gather "
+                   "parallelism": f"replicas x{n_gpus}, whole-sequence bin packing, gather of outputs to rank 0 "
+                                  f"({'copy-engine peer copies into symmetric memory' if type(batches[0].gatherer).__name__ == 'PeerGatherer' else 'NCCL send/recv'}) timed (the gather "
                                   f"of step i overlaps the kernels of steps i+1 and i+2; the last gathers' tail is added)"
                    if n_gpus > 1 else "single GPU"},
         "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms_per_step, "h2d_bytes_per_step": h2d,
@@ -521,11 +523,14 @@ def main():
     ap.add_argument("--workload", default="base", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--seqs", type=int, default=0, help="sequences per GPU (default: the workload's own count)")
+    ap.add_argument("--gather", default=None, choices=["peer", "nccl"],
+                    help="N > 1: how outputs reach rank 0 (default: copy-engine peer copies where available, else NCCL send/recv)")
     ap.add_argument("--total-seqs", type=int, default=0,
                     help="strong scaling: this many sequences in the global batch whatever --gpus (must divide evenly)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     w = WORKLOADS[args.workload]
+    w["gather"] = args.gather
     if args.seqs > 0:
         w["seqs"] = args.seqs
         w["desc"] += f" (--seqs {args.seqs})"

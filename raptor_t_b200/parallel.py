@@ -218,3 +218,143 @@ class RootGatherer:
         if self.cuda:
             torch.cuda.current_stream().wait_event(self.done[ticket])
         return self.out[ticket]
+
+
+class PeerGatherer:
+    """RootGatherer's job without kernels on the SMs: the root's result buffers live in symmetric memory
+    (every rank maps them), a sending rank copies each of its sequences straight into the root's buffer with
+    device-to-device copies (copy engines over NVLink), and hand-offs are 4-byte copies of a generation
+    number into the peer's flag words, waited for with stream memory operations.  Nothing of it occupies an
+    SM, so the compute kernels of the next steps keep all of them (NCCL's send/receive kernels wait for
+    their peer on SMs whose registers and shared memory the compute kernels want whole).
+
+    Same interface as RootGatherer (start / finish, `depth` buffers in rotation).  Flow control: a sender
+    writes buffer k of generation g only after the root has released generation g - depth of it (the root's
+    flag copy follows whatever consumed the buffer on the side stream, e.g. the copy to the host).
+    Needs CUDA, torch symmetric memory and the cuda-python driver bindings; `available()` says so."""
+
+    @staticmethod
+    def available():
+        try:
+            import torch.distributed._symmetric_memory  # noqa: F401
+            from cuda.bindings import driver  # noqa: F401
+            return torch.cuda.is_available()
+        except Exception:
+            return False
+
+    def __init__(self, assignment, lens_tokens, hidden, dtype, device, group=None, depth=2, root=0):
+        import torch.distributed._symmetric_memory as symm
+        from cuda.bindings import driver
+        self._drv = driver
+        self.group = group if group is not None else dist.group.WORLD
+        self.root = root
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.device = torch.device(device)
+        self.starts = np.concatenate([[0], np.cumsum(lens_tokens)]).astype(np.int64)
+        self.total = int(self.starts[-1])
+        self.lens = [int(n) for n in lens_tokens]
+        self.assignment = [list(a) for a in assignment]
+        self.is_root = self.rank == root
+        self.depth = depth
+        # result buffers: allocated on every rank (symmetric), used on the root
+        self._buf = symm.empty((depth, self.total, hidden), dtype=dtype, device=self.device)
+        self._hbuf = symm.rendezvous(self._buf, self.group.group_name)
+        self._root_buf = self._hbuf.get_buffer(root, (depth, self.total, hidden), dtype)
+        # flag words: [0 : world*depth] "rank r has filled buffer k" (read on the root),
+        #             [world*depth : world*depth + depth] "buffer k is free again" (read on the senders)
+        self._flags = symm.empty((self.world * depth + depth,), dtype=torch.int32, device=self.device)
+        self._flags.zero_()
+        self._hflags = symm.rendezvous(self._flags, self.group.group_name)
+        self._peer_flags = [self._hflags.get_buffer(r, (self.world * depth + depth,), torch.int32) for r in range(self.world)]
+        self._gen_limit = 1 << 16
+        self._gen_src = torch.arange(0, self._gen_limit, dtype=torch.int32, device=self.device)  # source of the 4-byte copies
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+        self.out = [self._buf[k] for k in range(depth)] if self.is_root else [None] * depth
+        self.side = torch.cuda.Stream(device=self.device)
+        self.done = [torch.cuda.Event() for _ in range(depth)]
+        self.n = 0
+
+    def _wait(self, flag_index, value):
+        addr = self._flags.data_ptr() + 4 * flag_index
+        err, = self._drv.cuStreamWaitValue32(self.side.cuda_stream, addr, value,
+                                             self._drv.CUstreamWaitValue_flags.CU_STREAM_WAIT_VALUE_GEQ)
+        if int(err) != 0:
+            raise RuntimeError(f"cuStreamWaitValue32 failed: {err}")
+
+    def _signal(self, peer, flag_index, value):
+        self._peer_flags[peer][flag_index:flag_index + 1].copy_(self._gen_src[value:value + 1], non_blocking=True)
+
+    def start(self, local_out, host_out=None):
+        if self.n // self.depth + 1 >= self._gen_limit:
+            self._restart()
+        k = self.n % self.depth
+        gen = self.n // self.depth + 1
+        self.n += 1
+        ready = torch.cuda.Event()
+        ready.record()
+        W, D = self.world, self.depth
+        with torch.cuda.stream(self.side):
+            self.side.wait_event(ready)
+            if self.is_root:
+                out = self._buf[k]
+                off = 0
+                for i in self.assignment[self.rank]:
+                    n, s0 = self.lens[i], int(self.starts[i])
+                    out[s0:s0 + n].copy_(local_out[off:off + n], non_blocking=True)
+                    off += n
+                for r in range(W):
+                    if r != self.rank:
+                        self._wait(r * D + k, gen)
+                if host_out is not None:
+                    host_out[: self.total].copy_(out, non_blocking=True)
+                self.done[k].record()
+                # the buffer may be refilled once this point of the side stream is reached; a caller that reads it
+                # on another stream does so between finish() and its next start(), `depth` gathers earlier
+                for r in range(W):
+                    if r != self.rank:
+                        self._signal(r, W * D + k, gen)
+            else:
+                if gen > 1:
+                    self._wait(W * D + k, gen - 1)
+                dst = self._root_buf[k]
+                off = 0
+                for i in self.assignment[self.rank]:
+                    n, s0 = self.lens[i], int(self.starts[i])
+                    dst[s0:s0 + n].copy_(local_out[off:off + n], non_blocking=True)
+                    off += n
+                self._signal(self.root, self.rank * D + k, gen)
+                self.done[k].record()
+        return k
+
+    def finish(self, ticket):
+        torch.cuda.current_stream().wait_event(self.done[ticket])
+        return self.out[ticket]
+
+    def _restart(self):
+        """Generation numbers are drawn from a table; when it is used up all ranks drain, clear their flag words and
+        start again at generation 1 (every rank reaches this at the same gather)."""
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+        self._flags.zero_()
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+        self.n = 0
+
+
+def make_root_gatherer(assignment, lens_tokens, hidden, dtype, device, group=None, depth=2, root=0, kind=None):
+    """PeerGatherer where it can be built (kind "peer"), RootGatherer (NCCL / gloo send-recv) otherwise."""
+    if kind == "peer":
+        return PeerGatherer(assignment, lens_tokens, hidden, dtype, device, group=group, depth=depth, root=root)
+    if kind is None and torch.device(device).type == "cuda" and PeerGatherer.available():
+        # every rank must take the same branch: agree on it
+        ok = torch.ones(1, device=device)
+        try:
+            g = PeerGatherer(assignment, lens_tokens, hidden, dtype, device, group=group, depth=depth, root=root)
+        except Exception:
+            g, ok = None, torch.zeros(1, device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+        if ok.item() > 0:
+            return g
+    return RootGatherer(assignment, lens_tokens, hidden, dtype, device, group=group, depth=depth, root=root)
